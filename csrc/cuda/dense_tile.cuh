@@ -1,0 +1,269 @@
+// Tile-level device code shared by the stand-alone encode/decode kernels and by
+// the fused ring / parameter-server kernels.
+//
+// A tile is kTile (4096) consecutive fp32 elements handled by one 256-thread
+// CTA: every thread keeps 16 elements in registers (four float4 at float4-index
+// j*256+tid), so the residual add, the per-tile scale or min/max reduction, the
+// quantisation and the residual write-back all happen on one pass over HBM
+// (12 B/element with error feedback, 4 B/element without).  The reference does
+// this with two synchronising thrust::reduce calls, a thrust::transform with
+// one thread per output byte and four host memcpys per tensor
+// (src/CompLL/GCGen/output/TernGradEncode/TernGradEncode_body.h:115-123).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "hipress/common.h"
+
+namespace hipress {
+
+constexpr int kThreads = 256;
+constexpr int kIter = kTile / (kThreads * 4);  // float4 per thread per tile
+static_assert(kIter * kThreads * 4 == kTile, "tile must split evenly");
+
+struct TileSmem {
+  alignas(16) uint8_t codes[kTile];  // staged code bytes, up to 8 bits/element
+  double red_d[kThreads / 32];
+  float red_a[kThreads / 32];
+  float red_b[kThreads / 32];
+};
+
+// ------------------------------------------------------------------ memory ops
+__device__ __forceinline__ void load_tile(const float* __restrict__ p, int m,
+                                          float (&x)[kIter][4]) {
+  const bool vec = (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+#pragma unroll
+  for (int j = 0; j < kIter; ++j) {
+    const int i0 = 4 * (j * kThreads + (int)threadIdx.x);
+    if (vec && i0 + 3 < m) {
+      const float4 v = *reinterpret_cast<const float4*>(p + i0);
+      x[j][0] = v.x; x[j][1] = v.y; x[j][2] = v.z; x[j][3] = v.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[j][e] = (i0 + e < m) ? p[i0 + e] : 0.0f;
+    }
+  }
+}
+
+__device__ __forceinline__ void store_tile(float* __restrict__ p, int m,
+                                           const float (&x)[kIter][4]) {
+  const bool vec = (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+#pragma unroll
+  for (int j = 0; j < kIter; ++j) {
+    const int i0 = 4 * (j * kThreads + (int)threadIdx.x);
+    if (vec && i0 + 3 < m) {
+      *reinterpret_cast<float4*>(p + i0) = make_float4(x[j][0], x[j][1], x[j][2], x[j][3]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (i0 + e < m) p[i0 + e] = x[j][e];
+    }
+  }
+}
+
+// Code fragment = the 4*B bits of the four elements of one float4.
+// Payload bytes that another GPU wrote are read with ld.global.cg (L2 only).
+template <int B>
+__device__ __forceinline__ uint32_t load_frag(const uint8_t* __restrict__ codes, int j, int m) {
+  const int f = j * kThreads + (int)threadIdx.x;
+  if (4 * f >= m) return 0u;
+  if (B == 1) {
+    const uint32_t b = __ldcg(codes + (f >> 1));
+    return (f & 1) ? (b >> 4) : (b & 15u);
+  } else if (B == 2) {
+    return __ldcg(codes + f);
+  } else if (B == 4) {
+    return __ldcg(reinterpret_cast<const unsigned short*>(codes) + f);
+  } else {
+    return __ldcg(reinterpret_cast<const unsigned int*>(codes) + f);
+  }
+}
+
+template <int B>
+__device__ __forceinline__ void stage_frags(uint8_t* sc, const uint32_t (&frag)[kIter]) {
+#pragma unroll
+  for (int j = 0; j < kIter; ++j) {
+    const int f = j * kThreads + (int)threadIdx.x;
+    if (B == 1) {
+      const uint32_t hi = __shfl_down_sync(0xffffffffu, frag[j], 1);
+      if (!(threadIdx.x & 1)) sc[f >> 1] = (uint8_t)(frag[j] | (hi << 4));
+    } else if (B == 2) {
+      sc[f] = (uint8_t)frag[j];
+    } else if (B == 4) {
+      reinterpret_cast<uint16_t*>(sc)[f] = (uint16_t)frag[j];
+    } else {
+      reinterpret_cast<uint32_t*>(sc)[f] = frag[j];
+    }
+  }
+}
+
+__device__ __forceinline__ int tile_code_bytes(int m, int bits) {
+  return (int)align_up(((uint64_t)m * bits + 7) / 8, 16);
+}
+
+// 16-byte stores; dst may be a peer GPU's memory (plain st.global over NVLink).
+__device__ __forceinline__ void copy_codes(uint8_t* __restrict__ dst, const uint8_t* sc,
+                                           int nbytes) {
+  for (int o = (int)threadIdx.x * 16; o < nbytes; o += kThreads * 16)
+    *reinterpret_cast<uint4*>(dst + o) = *reinterpret_cast<const uint4*>(sc + o);
+}
+
+// ------------------------------------------------------------- block reductions
+// All 256 threads must call; every thread returns the same value.
+__device__ __forceinline__ double block_sum(double v, TileSmem& s) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) s.red_d[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double t = 0.0;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) t += s.red_d[w];
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ void block_minmax(float& mn, float& mx, TileSmem& s) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s.red_a[threadIdx.x >> 5] = mn;
+    s.red_b[threadIdx.x >> 5] = mx;
+  }
+  __syncthreads();
+  mn = s.red_a[0];
+  mx = s.red_b[0];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) {
+    mn = fminf(mn, s.red_a[w]);
+    mx = fmaxf(mx, s.red_b[w]);
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------ algorithms
+// decode the four elements of fragment j into d[0..3]
+template <int ALG, int B>
+__device__ __forceinline__ void decode_frag(uint32_t frag, const float (&meta)[2], float tau,
+                                            float (&d)[4]) {
+  constexpr uint32_t mask = (1u << B) - 1u;
+  float gap = 0.0f;
+  if (ALG == kTernGrad) gap = tern_gap(meta[0], meta[1], B);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const uint32_t c = (frag >> (e * B)) & mask;
+    if (ALG == kOnebit) d[e] = onebit_value(c, meta[0]);
+    else if (ALG == kTbq) d[e] = tbq_value(c, tau);
+    else d[e] = tern_value(c, meta[0], gap);
+  }
+}
+
+// Quantise the register tile x (m valid elements).  On return frag[] holds the
+// code fragments (zero for elements past m), meta[] the tile metadata, and x the
+// quantisation error x - decode(code) of every valid element.
+template <int ALG, int B>
+__device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const DenseParams& P,
+                                            uint32_t tensor_id, uint64_t elem0, uint32_t salt,
+                                            TileSmem& s, float (&meta)[2],
+                                            uint32_t (&frag)[kIter]) {
+  meta[0] = 0.0f;
+  meta[1] = 0.0f;
+  if (ALG == kOnebit) {
+    double part = 0.0;
+#pragma unroll
+    for (int j = 0; j < kIter; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (4 * (j * kThreads + (int)threadIdx.x) + e < m) part += (double)fabsf(x[j][e]);
+    const double tot = block_sum(part, s);
+    meta[0] = (float)(tot / (double)m);
+  } else if (ALG == kTernGrad) {
+    float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kIter; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (4 * (j * kThreads + (int)threadIdx.x) + e < m) {
+          mn = fminf(mn, x[j][e]);
+          mx = fmaxf(mx, x[j][e]);
+        }
+    block_minmax(mn, mx, s);
+    meta[0] = mn;
+    meta[1] = mx;
+  }
+  float gap = 0.0f;
+  if (ALG == kTernGrad) gap = tern_gap(meta[0], meta[1], B);
+#pragma unroll
+  for (int j = 0; j < kIter; ++j) {
+    const int i0 = 4 * (j * kThreads + (int)threadIdx.x);
+    Philox4 rnd;
+    if (ALG == kTernGrad) {
+      const uint64_t ge = elem0 + (uint64_t)i0;
+      rnd = philox4x32_10((uint32_t)(ge >> 2), tensor_id, P.step, salt, P.seed_lo, P.seed_hi);
+    }
+    uint32_t f = 0u;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (i0 + e < m) {
+        uint32_t c;
+        float d;
+        if (ALG == kOnebit) {
+          c = onebit_code(x[j][e]);
+          d = onebit_value(c, meta[0]);
+        } else if (ALG == kTbq) {
+          c = tbq_code(x[j][e], P.tau);
+          d = tbq_value(c, P.tau);
+        } else {
+          c = tern_code(x[j][e], meta[0], gap, u01(rnd.v[e]), B);
+          d = tern_value(c, meta[0], gap);
+        }
+        f |= c << (e * B);
+        x[j][e] = x[j][e] - d;
+      }
+    }
+    frag[j] = f;
+  }
+}
+
+// Byte layout of one dense payload of `n_layout` elements (n_layout fixes where
+// the code region starts; fewer elements may actually be valid).
+struct PayloadView {
+  uint8_t* base;
+  float* meta;
+  uint8_t* codes;
+};
+__device__ __forceinline__ PayloadView payload_view(uint8_t* base, int alg, uint64_t n_layout) {
+  PayloadView v;
+  v.base = base;
+  v.meta = reinterpret_cast<float*>(base + 16);
+  v.codes = base + 16 + dense_meta_bytes(alg, n_layout);
+  return v;
+}
+
+__device__ __forceinline__ void write_header(uint8_t* base, uint32_t n, int alg, int bits,
+                                             float tau) {
+  WireHeader h;
+  h.n = n;
+  h.alg = (uint8_t)alg;
+  h.bitwidth = (uint8_t)bits;
+  h.flags = dense_meta_floats(alg) ? 1 : 0;
+  h.a = alg == kTbq ? tau : 0.0f;
+  h.b = kTile;
+  *reinterpret_cast<uint4*>(base) = *reinterpret_cast<const uint4*>(&h);
+}
+
+// read tile metadata that may have been written by a peer
+template <int ALG>
+__device__ __forceinline__ void load_meta(const float* meta, uint32_t t, float (&m)[2]) {
+  m[0] = 0.0f;
+  m[1] = 0.0f;
+  if (ALG == kOnebit) m[0] = __ldcg(meta + t);
+  if (ALG == kTernGrad) {
+    m[0] = __ldcg(meta + 2 * t);
+    m[1] = __ldcg(meta + 2 * t + 1);
+  }
+}
+
+}  // namespace hipress

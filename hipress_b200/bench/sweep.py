@@ -1,0 +1,120 @@
+"""Kernel sweep on one GPU: stand-alone encode / decode of the five algorithms and
+the fused ring / PS kernels with N emulated ranks, fp32 gradients of 4 KB - 1 GB
+(powers of 4), values N(0,1) seed 0.  Reports milliseconds, achieved GB/s over the
+algorithmic HBM bytes and the fraction of the measured copy bandwidth.
+
+    python -m hipress_b200.bench.sweep --what ops --out gpurun_out/sweep_ops.json
+    python -m hipress_b200.bench.sweep --what fused --ranks 8 --max-mb 256
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from ..ops import Compressor
+from ..parallel.fused import FusedDenseBucket
+from .timing import L2Flusher, measured_peaks, time_cuda
+
+ALGS = [("onebit", {}), ("tbq", {}), ("terngrad", {"bitwidth": 2}), ("dgc", {}), ("graddrop", {})]
+
+
+def algorithmic_bytes(c: Compressor, n: int, op: str) -> float:
+    """HBM bytes the op has to move at minimum."""
+    sp = c.spec
+    pay = c.payload_bytes(n)
+    if op == "decode":
+        return pay + 4.0 * n
+    if sp.sparse:
+        state = 20.0 if sp.name == "dgc" else 12.0  # read g,(u),v write (u),v
+        return state * n + pay
+    ef = 8.0 if "residual" in sp.state_names() else 0.0
+    return (4.0 + ef) * n + pay
+
+
+def sweep_ops(sizes, iters, out):
+    peaks = measured_peaks()
+    flush = L2Flusher()
+    for name, kw in ALGS:
+        c = Compressor(name, **kw)
+        for nbytes in sizes:
+            n = nbytes // 4
+            g = torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
+            st = c.new_state(n, "cuda")
+            pay = torch.empty(c.payload_bytes(n), dtype=torch.uint8, device="cuda")
+            ws = c.new_workspace("cuda")
+            res = torch.empty(n, device="cuda")
+            enc = time_cuda(lambda: c.encode(g, st, out=pay, workspace=ws), iters=iters, flush=flush)
+            dec = time_cuda(lambda: c.decode(pay, res), iters=iters, flush=flush)
+            for op, t in (("encode", enc), ("decode", dec)):
+                b = algorithmic_bytes(c, n, op)
+                gbs = b / (t["median_ms"] * 1e-3) / 1e9
+                row = {"alg": name, "op": op, "bytes": nbytes, "ms": round(t["median_ms"], 5),
+                       "min_ms": round(t["min_ms"], 5), "alg_gb": round(b / 1e9, 6),
+                       "gbs": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                       "peak_source": peaks["source"]}
+                out.append(row)
+                print(json.dumps(row), flush=True)
+            del g, st, pay, res
+
+
+def sweep_fused(sizes, iters, ranks, ctas, out):
+    peaks = measured_peaks()
+    flush = L2Flusher()
+    for topo in ("ring", "ps"):
+        for name, kw in ALGS[:3]:
+            c = Compressor(name, **kw)
+            ef = "residual" in c.spec.state_names()
+            for nbytes in sizes:
+                n = nbytes // 4
+                if n * 4 * ranks * 3 > 24e9:
+                    continue
+                b = FusedDenseBucket(c.spec, topo, [n], ranks, 0, ctas=ctas, emulate=True)
+                b.bind_local("cuda")
+                G = torch.randn(ranks, n, device="cuda",
+                                generator=torch.Generator("cuda").manual_seed(0))
+                Rr = torch.zeros(ranks, n, device="cuda") if ef else None
+                O = torch.empty(ranks, n, device="cuda")
+                t = time_cuda(lambda: b.launch([G], [Rr] if ef else None, [O]), iters=iters,
+                              flush=flush)
+                b.check_status()
+                # all emulated ranks share one GPU's HBM: bytes = ranks * per-rank bytes
+                per_rank = (4.0 + (8.0 if ef else 0.0) + 4.0) * n
+                gbs = per_rank * ranks / (t["median_ms"] * 1e-3) / 1e9
+                row = {"kernel": f"{topo}_{name}", "ranks_emulated": ranks, "bytes": nbytes,
+                       "ms": round(t["median_ms"], 5), "gbs_all_ranks": round(gbs, 1),
+                       "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "ctas_per_rank": b.ctas,
+                       "peak_source": peaks["source"]}
+                out.append(row)
+                print(json.dumps(row), flush=True)
+                del b, G, Rr, O
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", choices=["ops", "fused", "all"], default="all")
+    ap.add_argument("--min-kb", type=int, default=4)
+    ap.add_argument("--max-mb", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--ranks", type=int, default=8)
+    ap.add_argument("--ctas", type=int, default=72, help="CTAs per emulated rank")
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args(argv)
+    sizes = []
+    s = a.min_kb * 1024
+    while s <= a.max_mb * 1024 * 1024:
+        sizes.append(s)
+        s *= 4
+    out = []
+    if a.what in ("ops", "all"):
+        sweep_ops(sizes, a.iters, out)
+    if a.what in ("fused", "all"):
+        sweep_fused(sizes, a.iters, a.ranks, a.ctas, out)
+    if a.out:
+        with open(a.out, "w") as f:
+            json.dump(out, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,100 @@
+"""Fused ring / PS kernels with all N ranks emulated by one cooperative launch on
+one GPU, against the lock-step simulation built from CPU-oracle primitives."""
+import pytest
+import torch
+
+from hipress_b200.ops import Compressor
+from hipress_b200.parallel.fused import FusedDenseBucket, HipressTimeoutError
+from hipress_b200.parallel.simulate import chunk_elems, simulate_ps, simulate_ring
+
+pytestmark = pytest.mark.gpu
+
+ALGS = [("tbq", {}), ("onebit", {}), ("terngrad", {"bitwidth": 2}), ("terngrad", {"bitwidth": 8})]
+
+
+def _run(topology, name, kw, N, sizes, steps=2, ctas=8):
+    torch.manual_seed(1234 + N)
+    c = Compressor(name, **kw)
+    ef = "residual" in c.spec.state_names()
+    bucket = FusedDenseBucket(c.spec, topology, sizes, N, 0, ctas=ctas, emulate=True).bind_local("cuda")
+    total = sum(sizes)
+    G = torch.zeros(N, total, device="cuda")
+    Rr = torch.zeros(N, total, device="cuda") if ef else None
+    O = torch.zeros(N, total, device="cuda")
+    chunks = [chunk_elems(s, N) for s in sizes]
+    SR = torch.zeros(N, sum(chunks), device="cuda") if (ef and topology == "ps") else None
+    offs = [sum(sizes[:i]) for i in range(len(sizes))]
+    coffs = [sum(chunks[:i]) for i in range(len(sizes))]
+    cpu_states = [[c.new_state(s, "cpu") for s in sizes] for _ in range(N)]
+    cpu_sstates = [[({"residual": torch.zeros(ch)} if SR is not None else {}) for ch in chunks]
+                   for _ in range(N)]
+    for step in range(steps):
+        Gc = torch.randn(N, total) * 0.02
+        G.copy_(Gc)
+        grads = [G[:, o:o + s] for o, s in zip(offs, sizes)]
+        res = [Rr[:, o:o + s] for o, s in zip(offs, sizes)] if ef else None
+        outs = [O[:, o:o + s] for o, s in zip(offs, sizes)]
+        srs = [SR[:, o:o + ch] for o, ch in zip(coffs, chunks)] if SR is not None else None
+        bucket.launch(grads, res, outs, srs, step=step, salt=0, tensor_ids=list(range(len(sizes))))
+        torch.cuda.synchronize()
+        bucket.check_status()
+        for i, (o, s) in enumerate(zip(offs, sizes)):
+            gl = [Gc[r, o:o + s].contiguous() for r in range(N)]
+            sts = [cpu_states[r][i] for r in range(N)]
+            if topology == "ring":
+                ref = simulate_ring(c, gl, sts, step=step, tensor_id=i)
+            else:
+                ref = simulate_ps(c, gl, sts, [cpu_sstates[r][i] for r in range(N)], step=step,
+                                  tensor_id=i)
+            for r in range(N):
+                got = O[r, o:o + s].cpu()
+                assert torch.allclose(got, ref[r], rtol=1e-5, atol=1e-9), \
+                    f"{topology} {name} N={N} step={step} tensor={i} rank={r}: " \
+                    f"{(got - ref[r]).abs().max().item()}"
+                assert torch.equal(O[r, o:o + s], O[0, o:o + s]), "ranks disagree"
+                if ef:
+                    assert torch.allclose(Rr[r, o:o + s].cpu(), sts[r]["residual"], rtol=1e-5, atol=1e-8)
+
+
+@pytest.mark.parametrize("N", [1, 2, 4, 8])
+@pytest.mark.parametrize("name,kw", ALGS)
+def test_ring_emulated(name, kw, N):
+    _run("ring", name, kw, N, [70001, 4096, 300, 1 << 17])
+
+
+@pytest.mark.parametrize("N", [1, 2, 4, 8])
+@pytest.mark.parametrize("name,kw", ALGS)
+def test_ps_emulated(name, kw, N):
+    _run("ps", name, kw, N, [70001, 4096, 300, 1 << 17])
+
+
+def test_mean_of_many_steps_tracks_uncompressed_average():
+    """Error feedback: over many steps the compressed ring delivers the same total."""
+    torch.manual_seed(0)
+    N, n = 4, 50000
+    c = Compressor("tbq", threshold=0.01)
+    b = FusedDenseBucket(c.spec, "ring", [n], N, 0, ctas=4, emulate=True).bind_local("cuda")
+    G = torch.zeros(N, n, device="cuda")
+    Rr = torch.zeros(N, n, device="cuda")
+    O = torch.zeros(N, n, device="cuda")
+    tot_ref = torch.zeros(n, device="cuda")
+    tot = torch.zeros(n, device="cuda")
+    for step in range(30):
+        G.normal_(0, 0.004)
+        tot_ref += G.mean(0)
+        b.launch([G], [Rr], [O], step=step)
+        tot += O[0]
+    torch.cuda.synchronize()
+    b.check_status()
+    # what has not been delivered yet sits in the residuals
+    pending = Rr.sum(0) / N
+    assert torch.allclose(tot + pending, tot_ref, atol=2e-6)
+
+
+def test_residency_guard():
+    c = Compressor("tbq")
+    b = FusedDenseBucket(c.spec, "ring", [1 << 24], 8, 0, ctas=4000, emulate=True).bind_local("cuda")
+    G = torch.zeros(8, 1 << 24, device="cuda")
+    from hipress_b200._native.lib import NativeLibraryError
+    with pytest.raises(NativeLibraryError):
+        b.launch([G], None, [G])
