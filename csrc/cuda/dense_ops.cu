@@ -21,7 +21,13 @@ dense_encode_kernel(const float* __restrict__ g, float* __restrict__ r,
   const uint32_t tiles = (uint32_t)num_tiles(n);
   PayloadView ov = payload_view(out, ALG, n);
   PayloadView iv = payload_view(const_cast<uint8_t*>(in_payload), ALG, n);
-  if (blockIdx.x == 0 && threadIdx.x == 0) write_header(out, n, ALG, B, P.tau);
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) write_header(out, n, ALG, B, P.tau);
+    // zero the padding behind the tile metadata so payload bytes are deterministic
+    const uint32_t used = tiles * dense_meta_floats(ALG);
+    const uint32_t padded = (uint32_t)(dense_meta_bytes(ALG, n) / 4);
+    for (uint32_t i = used + threadIdx.x; i < padded; i += kThreads) ov.meta[i] = 0.0f;
+  }
   for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
     const uint32_t start = t * kTile;
     const int m = (int)min((uint32_t)kTile, n - start);

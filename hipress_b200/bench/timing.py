@@ -24,13 +24,18 @@ def measured_peaks() -> dict:
 
 
 class L2Flusher:
-    """Writes a buffer larger than the 126 MB L2 so the next timed run starts cold."""
+    """Writes a buffer larger than the 126 MB L2 so the next timed run starts cold,
+    then reads a second one so the cache is left holding clean lines (otherwise
+    the timed kernel also pays for writing the flush buffer's dirty lines back)."""
 
     def __init__(self, device="cuda", mbytes=256):
-        self.buf = torch.empty(mbytes * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+        self.buf = torch.zeros(mbytes * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+        self.rd = torch.zeros(mbytes * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+        self.sink = torch.zeros((), dtype=torch.float32, device=device)
 
     def __call__(self):
         self.buf.add_(1.0)
+        self.sink = self.rd.sum()
 
 
 def time_cuda(fn, *, warmup=3, iters=10, flush: L2Flusher | None = None, setup=None):

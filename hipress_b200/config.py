@@ -1,0 +1,79 @@
+"""Run-time configuration: one dataclass fed by command-line flags with the same
+spellings the reference launchers use (``--topo``, ``--comp-alg``,
+``--comp-threshold``, ``--comprplan`` for the MXNet script, README.md:160-169;
+``--algorithm`` for the PyTorch script, README.md:186) and by ``HIPRESS_*``
+environment variables."""
+from __future__ import annotations
+
+import argparse
+import os
+from dataclasses import dataclass, field, fields
+
+
+@dataclass
+class HipressConfig:
+    algorithm: str = "tbq"            # onebit | tbq | terngrad | dgc | graddrop | none
+    topology: str = "ring"            # ring | ps
+    comp_threshold: int = 262144      # gradients with fewer elements are not compressed
+    plan: str | None = None           # SeCoPa plan file (overrides comp_threshold)
+    threshold: float = 0.01           # tbq
+    bitwidth: int | None = None       # terngrad
+    ratio: float = 0.001              # dgc / graddrop
+    momentum: float = 0.9             # dgc momentum correction
+    seed: int = 0
+    backend: str = "auto"             # auto | fused | host | allreduce
+    bucket_bytes: int = 64 << 20      # gradient bytes per fused launch
+    plain_bucket_bytes: int = 32 << 20
+    ctas: int = 64                    # CTAs of a fused kernel while it overlaps backward
+    timeout_s: float = 10.0           # bound of every device-side wait
+    server_residual: bool = True      # PS: error feedback on the re-encode at the owner
+    overlap: bool = True              # launch buckets from gradient hooks during backward
+    log_level: str = field(default_factory=lambda: os.environ.get("HIPRESS_LOG_LEVEL", "INFO"))
+
+    def algorithm_kwargs(self) -> dict:
+        return dict(threshold=self.threshold, bitwidth=self.bitwidth, ratio=self.ratio,
+                    momentum=self.momentum, seed=self.seed)
+
+    @staticmethod
+    def from_env(**overrides) -> "HipressConfig":
+        cfg = HipressConfig()
+        for f in fields(HipressConfig):
+            v = os.environ.get("HIPRESS_" + f.name.upper())
+            if v is None:
+                continue
+            cur = getattr(cfg, f.name)
+            if isinstance(cur, bool):
+                setattr(cfg, f.name, v.lower() in ("1", "true", "yes"))
+            elif isinstance(cur, int):
+                setattr(cfg, f.name, int(v))
+            elif isinstance(cur, float):
+                setattr(cfg, f.name, float(v))
+            else:
+                setattr(cfg, f.name, v)
+        for k, v in overrides.items():
+            if v is not None:
+                setattr(cfg, k, v)
+        return cfg
+
+
+def add_hipress_args(ap: argparse.ArgumentParser) -> argparse.ArgumentParser:
+    g = ap.add_argument_group("hipress")
+    g.add_argument("--topo", "--topology", dest="topo", default="Ring",
+                   help="CaSync topology: PS or Ring")
+    g.add_argument("--comp-alg", "--comp_alg", "--algorithm", dest="comp_alg", default="tbq",
+                   help="onebit | tbq | terngrad | dgc | graddrop | none")
+    g.add_argument("--comp-threshold", dest="comp_threshold", type=int, default=262144,
+                   help="compress gradients with at least this many elements")
+    g.add_argument("--comprplan", default=None, help="SeCoPa plan file (name,size,y|n,K rows)")
+    g.add_argument("--threshold", type=float, default=0.01, help="tbq threshold")
+    g.add_argument("--bitwidth", type=int, default=None, help="terngrad bits per element")
+    g.add_argument("--ratio", type=float, default=0.001, help="dgc / graddrop send ratio")
+    g.add_argument("--sync-backend", default="auto", choices=["auto", "fused", "host", "allreduce"])
+    return ap
+
+
+def config_from_args(a) -> HipressConfig:
+    return HipressConfig.from_env(
+        algorithm=a.comp_alg.lower(), topology=a.topo.lower(), comp_threshold=a.comp_threshold,
+        plan=a.comprplan, threshold=a.threshold, bitwidth=a.bitwidth, ratio=a.ratio,
+        backend=a.sync_backend)

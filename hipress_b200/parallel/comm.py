@@ -1,0 +1,103 @@
+"""Process bootstrap: one process per GPU over ``torch.distributed`` (NCCL on a GPU
+box, gloo on CPU), Horovod-style module functions ``init / rank / size /
+local_rank / shutdown``.  A lone process with no launcher environment runs as a
+world of one without creating a process group."""
+from __future__ import annotations
+
+import datetime
+import os
+
+import torch
+import torch.distributed as dist
+
+_state = {"init": False, "rank": 0, "size": 1, "local_rank": 0, "own_pg": False, "device": None}
+
+
+def init(backend: str | None = None, timeout_s: float = 600.0):
+    """Join the job described by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR /
+    MASTER_PORT (as set by ``torch.distributed.run``)."""
+    if _state["init"]:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank_ = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    use_cuda = torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(local % torch.cuda.device_count())
+        _state["device"] = torch.device("cuda", torch.cuda.current_device())
+    else:
+        _state["device"] = torch.device("cpu")
+    if dist.is_initialized():
+        world, rank_ = dist.get_world_size(), dist.get_rank()
+    elif world > 1 or "MASTER_ADDR" in os.environ and "RANK" in os.environ:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        be = backend or ("nccl" if use_cuda else "gloo")
+        kw = {}
+        if be == "nccl":
+            kw["device_id"] = _state["device"]
+        dist.init_process_group(be, rank=rank_, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kw)
+        _state["own_pg"] = True
+    _state.update(init=True, rank=rank_, size=world, local_rank=local)
+
+
+def shutdown():
+    if _state["own_pg"] and dist.is_initialized():
+        dist.destroy_process_group()
+    _state.update(init=False, rank=0, size=1, local_rank=0, own_pg=False)
+
+
+def is_initialized() -> bool:
+    return _state["init"]
+
+
+def rank() -> int:
+    return _state["rank"]
+
+
+def size() -> int:
+    return _state["size"]
+
+
+def local_rank() -> int:
+    return _state["local_rank"]
+
+
+def device() -> torch.device:
+    return _state["device"] or torch.device("cuda" if torch.cuda.is_available() else "cpu")
+
+
+def barrier():
+    if size() > 1:
+        dist.barrier()
+
+
+def broadcast_parameters(params, root_rank: int = 0):
+    """Broadcast a ``state_dict`` or ``named_parameters`` from root to every rank."""
+    if size() == 1:
+        return
+    items = params.items() if isinstance(params, dict) else params
+    for _, p in items:
+        if torch.is_tensor(p):
+            dist.broadcast(p.data if hasattr(p, "data") else p, root_rank)
+
+
+def broadcast_optimizer_state(optimizer, root_rank: int = 0):
+    """Broadcast the tensors of an optimizer's state from root to every rank."""
+    if size() == 1:
+        return
+    opt = getattr(optimizer, "optimizer", optimizer)
+    obj = [opt.state_dict() if rank() == root_rank else None]
+    dist.broadcast_object_list(obj, src=root_rank)
+    if rank() != root_rank:
+        opt.load_state_dict(obj[0])
+
+
+def allreduce_(t: torch.Tensor, average: bool = True):
+    """Plain (uncompressed) in-place all-reduce."""
+    if size() > 1:
+        dist.all_reduce(t)
+        if average:
+            t.div_(size())
+    return t
