@@ -1,0 +1,22 @@
+"""hipress_b200: compression-aware gradient synchronisation for data-parallel
+PyTorch training on one NVSwitch box of B200 GPUs.
+
+Typical use (one process per GPU, launched with ``python -m torch.distributed.run``)::
+
+    import hipress_b200 as hp
+    hp.init()
+    opt = hp.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.01),
+                                  named_parameters=model.named_parameters(),
+                                  algorithm="tbq", topology="ring", comp_threshold=262144)
+    hp.broadcast_parameters(model.state_dict(), root_rank=0)
+    loss.backward(); opt.step(); opt.zero_grad()
+"""
+from .config import HipressConfig, add_hipress_args, config_from_args  # noqa: F401
+from .parallel.comm import (allreduce_, barrier, broadcast_optimizer_state,  # noqa: F401
+                            broadcast_parameters, device, init, is_initialized, local_rank, rank,
+                            shutdown, size)
+from .parallel.optimizer import DistributedOptimizer  # noqa: F401
+from .parallel.engine import GradSyncEngine  # noqa: F401
+from .ops import Compressor, get_algorithm, algorithm_names  # noqa: F401
+
+__version__ = "0.1.0"

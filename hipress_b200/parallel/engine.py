@@ -1,0 +1,463 @@
+"""CaSync runtime: turns the parameters of a model into buckets, launches each
+bucket's synchronisation as soon as its gradients exist (from autograd hooks, on a
+communication stream that overlaps the rest of backward) and hands averaged
+gradients to the optimizer.
+
+Per gradient the plan decides compressed or not (SeCoPa plan file or a size
+threshold) and the number of partitions K.  Compressed gradients go through
+
+* ``fused``  : one persistent sm_100a kernel per bucket (encode + peer-to-peer
+               transfer + decode-aggregate, csrc/cuda/fused_dense.cu); sparse
+               algorithms use the fused sparse kernels when present, else ``host``;
+* ``host``   : the same schedule from separate encode / decode calls around
+               ``torch.distributed`` messages (CPU/gloo ranks and the unfused GPU
+               baseline);
+* ``allreduce``: no compression, plain all-reduce (the uncompressed baseline).
+
+Uncompressed gradients always use a bucketed plain all-reduce, as in the
+reference ("PS-Lite and NCCL are used", README.md:153 of mark14wu/hipress).
+Every rank launches buckets in the same fixed order; the order of parameter names
+is checked across ranks once at start-up, so no per-step negotiation is needed
+(the reference inherits Horovod's background coordinator for that).
+"""
+from __future__ import annotations
+
+import logging
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..config import HipressConfig
+from ..ops.algorithms import get_algorithm
+from ..ops.compressor import TILE, Compressor
+from ..secopa.planner import read_plan
+from . import comm
+from .host_schedule import HostSchedule, SegView
+from .simulate import chunk_elems
+
+log = logging.getLogger("hipress")
+MAX_SEGS = 40
+
+
+@dataclass
+class Entry:
+    name: str
+    param: torch.nn.Parameter
+    numel: int
+    compress: bool
+    partitions: int
+    index: int
+    state: dict = field(default_factory=dict)         # name -> flat fp32 [numel]
+    server_state: list = field(default_factory=list)  # per partition: dict of owner-side state
+
+
+@dataclass
+class Segment:
+    entry: Entry
+    lo: int
+    hi: int
+    part: int
+
+    @property
+    def n(self):
+        return self.hi - self.lo
+
+    @property
+    def seg_id(self):
+        return self.entry.index * 64 + self.part
+
+
+@dataclass
+class Bucket:
+    index: int
+    fused: bool
+    entries: list = field(default_factory=list)
+    segs: list = field(default_factory=list)
+    pending: int = 0
+    launched: bool = False
+    impl: object = None
+    flat: torch.Tensor | None = None
+    work: object = None
+
+
+def _flat(t: torch.Tensor) -> torch.Tensor:
+    """Memory-order 1-D view of a dense tensor (any memory format)."""
+    if t.is_contiguous():
+        return t.view(-1)
+    return t.as_strided((t.numel(),), (1,))
+
+
+def split_partitions(n: int, k: int):
+    """k contiguous parts with tile-aligned boundaries (fewer when n is small)."""
+    k = max(1, min(k, (n + TILE - 1) // TILE))
+    per = ((n + k - 1) // k + TILE - 1) // TILE * TILE
+    out, lo = [], 0
+    while lo < n:
+        out.append((lo, min(n, lo + per)))
+        lo += per
+    return out
+
+
+class GradSyncEngine:
+    def __init__(self, named_parameters, config: HipressConfig | None = None, group=None,
+                 backward_passes_per_step: int = 1):
+        self.cfg = cfg = config or HipressConfig()
+        self.passes = max(1, int(backward_passes_per_step))
+        if not comm.is_initialized():
+            comm.init()
+        self.N, self.R, self.group = comm.size(), comm.rank(), group
+        named = [(n, p) for n, p in named_parameters if p.requires_grad]
+        if not named:
+            raise ValueError("no trainable parameters")
+        self.device = named[0][1].device
+        self.on_cuda = self.device.type == "cuda"
+        self.compress = cfg.algorithm not in ("none", None, "")
+        self.comp = Compressor(get_algorithm(cfg.algorithm, **cfg.algorithm_kwargs())) \
+            if self.compress else None
+        backend = cfg.backend
+        if backend == "auto":
+            backend = "fused" if self.on_cuda else "host"
+        if backend == "fused" and not self.on_cuda:
+            raise ValueError("the fused backend needs CUDA tensors")
+        if not self.compress:
+            backend = "allreduce"
+        self.backend = backend
+        self.step_no = 0
+        self.entries = self._make_entries(named)
+        self._check_order()
+        self.buckets = self._make_buckets()
+        self._alloc_state()
+        self.comm_stream = torch.cuda.Stream(priority=-1) if self.on_cuda else None
+        self.arena = None
+        self._setup_backend()
+        self._next = 0
+        self._hooks = []
+        self._by_param = {}
+        for b in self.buckets:
+            for e in b.entries:
+                self._by_param[e.param] = b
+        if cfg.overlap:
+            for e in self.entries:
+                self._hooks.append(e.param.register_post_accumulate_grad_hook(self._on_grad))
+        self._begin()
+        self.launch_count = 0
+        self.bytes_sent = 0
+
+    # ------------------------------------------------------------------ plan
+    def _make_entries(self, named):
+        cfg = self.cfg
+        plan = read_plan(cfg.plan) if cfg.plan else None
+        entries = []
+        for i, (name, p) in enumerate(named):
+            n = p.numel()
+            if not self.compress:
+                c, k = False, 1
+            elif plan is not None and name in plan:
+                size, c, k = plan[name]
+                if size != n:
+                    raise ValueError(f"plan row {name}: size {size} != parameter size {n}")
+            else:
+                if plan is not None:
+                    log.warning("gradient %s is not in the plan; using the size threshold", name)
+                c, k = n >= cfg.comp_threshold, 1
+            entries.append(Entry(name, p, n, bool(c), max(1, int(k)), i))
+        return entries
+
+    def _check_order(self):
+        """All ranks must register the same parameters in the same order."""
+        if self.N == 1:
+            return
+        mine = [(e.name, e.numel, e.compress, e.partitions) for e in self.entries]
+        every = [None] * self.N
+        dist.all_gather_object(every, mine, group=self.group)
+        for q, other in enumerate(every):
+            if other != mine:
+                raise RuntimeError(f"rank {self.R} and rank {q} disagree on the gradient list or plan")
+
+    def _make_buckets(self):
+        cfg = self.cfg
+        buckets, cur_f, cur_p = [], None, None
+        bytes_f = bytes_p = 0
+
+        def close(which):
+            nonlocal cur_f, cur_p, bytes_f, bytes_p
+            if which == "f" and cur_f is not None:
+                buckets.append(cur_f)
+                cur_f, bytes_f = None, 0
+            if which == "p" and cur_p is not None:
+                buckets.append(cur_p)
+                cur_p, bytes_p = None, 0
+
+        # gradients become ready roughly in reverse registration order
+        for e in reversed(self.entries):
+            if e.compress and self.backend != "allreduce":
+                parts = split_partitions(e.numel, e.partitions)
+                if cur_f is not None and (len(cur_f.segs) + len(parts) > MAX_SEGS
+                                          or bytes_f + 4 * e.numel > cfg.bucket_bytes):
+                    close("f")
+                if cur_f is None:
+                    cur_f = Bucket(0, True)
+                while len(parts) > MAX_SEGS:  # a tensor alone in its bucket: fewer, larger parts
+                    parts = split_partitions(e.numel, len(parts) // 2)
+                cur_f.entries.append(e)
+                cur_f.segs += [Segment(e, lo, hi, i) for i, (lo, hi) in enumerate(parts)]
+                bytes_f += 4 * e.numel
+            else:
+                if cur_p is not None and bytes_p + 4 * e.numel > cfg.plain_bucket_bytes:
+                    close("p")
+                if cur_p is None:
+                    cur_p = Bucket(0, False)
+                cur_p.entries.append(e)
+                bytes_p += 4 * e.numel
+        # order buckets by when they complete: backward produces gradients in
+        # descending registration order, so a bucket is complete once its
+        # lowest-index entry is; launch order must follow completion order
+        rest = [b for b in (cur_f, cur_p) if b is not None]
+        allb = sorted(buckets + rest, key=lambda b: -min(x.index for x in b.entries))
+        for i, b in enumerate(allb):
+            b.index = i
+        return allb
+
+    def _alloc_state(self):
+        if not self.compress:
+            return
+        sp = self.comp.spec
+        for b in self.buckets:
+            if not b.fused:
+                continue
+            for e in b.entries:
+                e.state = {k: torch.zeros(e.numel, dtype=torch.float32, device=self.device)
+                           for k in sp.state_names()}
+            for s in b.segs:
+                sst = {}
+                if self.cfg.topology == "ps" and self.cfg.server_residual and \
+                        (sp.sparse or "residual" in sp.state_names()):
+                    sst = {"residual": torch.zeros(chunk_elems(s.n, self.N), dtype=torch.float32,
+                                                   device=self.device)}
+                s.entry.server_state.append(sst)
+
+    # --------------------------------------------------------------- backends
+    def _setup_backend(self):
+        cfg = self.cfg
+        fused_buckets = [b for b in self.buckets if b.fused]
+        self._host = None
+        use_fused_kernels = self.backend == "fused" and self.compress and not self.comp.spec.sparse
+        if self.backend == "fused" and self.compress and self.comp.spec.sparse:
+            use_fused_kernels = self._setup_fused_sparse(fused_buckets)
+        if use_fused_kernels and not self.comp.spec.sparse:
+            from .fused import FusedDenseBucket
+            from .symm import SymmetricArena
+            impls = [FusedDenseBucket(self.comp.spec, cfg.topology, [s.n for s in b.segs], self.N,
+                                      self.R, ctas=cfg.ctas, timeout_s=cfg.timeout_s)
+                     for b in fused_buckets]
+            total = sum(i.region_bytes() for i in impls) + 4096
+            self.arena = SymmetricArena(total, self.group)
+            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            for b, impl in zip(fused_buckets, impls):
+                impl.bind(self.arena.carve(impl.region_bytes()), self.status)
+                b.impl = impl
+            self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+            self._status_event = None
+        elif fused_buckets and not use_fused_kernels:
+            self._host = HostSchedule(self.comp, cfg.topology, self.group)
+        for b in self.buckets:
+            if not b.fused and self.N > 1:
+                b.flat = torch.zeros(sum(e.numel for e in b.entries), dtype=torch.float32,
+                                     device=self.device)
+
+    def _setup_fused_sparse(self, fused_buckets) -> bool:
+        try:
+            from .fused_sparse import FusedSparseBucket  # noqa: F401
+        except ImportError:
+            return False
+        from .fused_sparse import setup_engine_buckets
+        return setup_engine_buckets(self, fused_buckets)
+
+    # ------------------------------------------------------------------ hooks
+    def _begin(self):
+        for b in self.buckets:
+            b.pending = len(b.entries) * self.passes
+            b.launched = False
+        self._next = 0
+
+    def _on_grad(self, param):
+        b = self._by_param[param]
+        b.pending -= 1
+        if b.pending == 0:
+            self._launch_ready()
+
+    def _launch_ready(self):
+        """Launch buckets strictly in index order (every rank issues the same
+        sequence), as far as their gradients are complete."""
+        while self._next < len(self.buckets) and self.buckets[self._next].pending <= 0:
+            self._launch(self.buckets[self._next])
+            self._next += 1
+
+    def _grad(self, e: Entry) -> torch.Tensor:
+        p = e.param
+        if p.grad is None:
+            p.grad = torch.zeros_like(p, memory_format=torch.preserve_format)
+        g = p.grad
+        if g.dtype != torch.float32:
+            raise TypeError(f"gradient of {e.name} is {g.dtype}; fp32 gradients are required")
+        if not (g.is_contiguous() or g.is_contiguous(memory_format=torch.channels_last)):
+            p.grad = g = g.contiguous()
+        return g
+
+    def _launch(self, b: Bucket):
+        b.launched = True
+        if self.on_cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self.comm_stream.wait_event(ev)
+            ctx = torch.cuda.stream(self.comm_stream)
+        else:
+            import contextlib
+            ctx = contextlib.nullcontext()
+        with ctx:
+            if b.fused:
+                self._launch_fused(b)
+            else:
+                self._launch_plain(b)
+
+    def _launch_fused(self, b: Bucket):
+        grads = {id(e): self._grad(e) for e in b.entries}
+        if b.impl is not None:
+            g_ptrs, r_ptrs, sr_ptrs, ids = [], [], [], []
+            rname = "residual"
+            for s in b.segs:
+                e = s.entry
+                base = grads[id(e)].data_ptr()
+                g_ptrs.append(base + 4 * s.lo)
+                r = e.state.get(rname)
+                r_ptrs.append(None if r is None else r.data_ptr() + 4 * s.lo)
+                sst = e.server_state[s.part] if e.server_state else {}
+                sr = sst.get("residual")
+                sr_ptrs.append(None if sr is None else sr.data_ptr())
+                ids.append(s.seg_id)
+            b.impl.launch_ptrs(g_ptrs, r_ptrs, g_ptrs, sr_ptrs, step=self.step_no, tensor_ids=ids,
+                               stream=self.comm_stream)
+            self.launch_count += 1
+        else:
+            views = []
+            for s in b.segs:
+                e = s.entry
+                fg = _flat(grads[id(e)])
+                views.append(SegView(fg[s.lo:s.hi], {k: v[s.lo:s.hi] for k, v in e.state.items()},
+                                     e.server_state[s.part] if e.server_state else {}, s.seg_id))
+            self._host.sync(views, step=self.step_no)
+
+    def _launch_plain(self, b: Bucket):
+        if self.N == 1:
+            return
+        grads = [self._grad(e) for e in b.entries]
+        torch.cat([g.reshape(-1) for g in grads], out=b.flat)
+        b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
+
+    def _finish_plain(self, b: Bucket):
+        if self.N == 1 or b.work is None:
+            return
+        b.work.wait()
+        b.work = None
+        b.flat.div_(self.N)
+        off = 0
+        for e in b.entries:
+            e.param.grad.copy_(b.flat[off:off + e.numel].view_as(e.param.grad))
+            off += e.numel
+
+    # ------------------------------------------------------------- step ends
+    def synchronize(self):
+        """Launch whatever has not been launched, then make the current stream
+        wait for every bucket.  Gradients are averaged in place afterwards."""
+        for b in self.buckets[self._next:]:
+            self._launch(b)
+        self._next = len(self.buckets)
+        if self.on_cuda:
+            with torch.cuda.stream(self.comm_stream):
+                for b in self.buckets:
+                    if not b.fused:
+                        self._finish_plain(b)
+                if self.arena is not None:
+                    self._poll_status()
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        else:
+            for b in self.buckets:
+                if not b.fused:
+                    self._finish_plain(b)
+        self.step_no += 1
+        self._begin()
+
+    def _poll_status(self):
+        """Asynchronous read of the kernels' status words; a timeout recorded in
+        one step is raised at the next synchronize (or by check())."""
+        from .fused import HipressTimeoutError, decode_status
+        if self._status_event is not None and self._status_event.query():
+            words = [w & 0xFFFFFFFF for w in self._status_host.tolist()]
+            if any(words):
+                self.status.zero_()
+                raise HipressTimeoutError(f"rank {self.R}: " + decode_status(words[0]))
+        self._status_host.copy_(self.status, non_blocking=True)
+        self._status_event = torch.cuda.Event()
+        self._status_event.record(self.comm_stream)
+
+    def check(self):
+        """Blocking check of the device status words."""
+        if self.arena is None:
+            return
+        from .fused import HipressTimeoutError, decode_status
+        torch.cuda.synchronize()
+        words = [w & 0xFFFFFFFF for w in self.status.cpu().tolist()]
+        if any(words):
+            self.status.zero_()
+            raise HipressTimeoutError(f"rank {self.R}: " + decode_status(words[0]))
+
+    # ------------------------------------------------------------ checkpoint
+    def state_dict(self) -> dict:
+        """Per-rank compressor state keyed by parameter name."""
+        out = {}
+        for e in self.entries:
+            if not e.state and not any(e.server_state):
+                continue
+            d = {k: v.detach().cpu().clone() for k, v in e.state.items()}
+            for i, sst in enumerate(e.server_state):
+                for k, v in sst.items():
+                    d[f"server_{k}.{i}"] = v.detach().cpu().clone()
+            d["step"] = self.step_no
+            out[e.name] = d
+        return {"world_size": self.N, "rank": self.R, "algorithm": self.cfg.algorithm,
+                "topology": self.cfg.topology, "step": self.step_no, "tensors": out}
+
+    def load_state_dict(self, sd: dict):
+        self.step_no = int(sd.get("step", 0))
+        if sd.get("world_size") != self.N or sd.get("algorithm") != self.cfg.algorithm:
+            log.warning("compressor state was saved for world size %s / %s; residuals dropped",
+                        sd.get("world_size"), sd.get("algorithm"))
+            return
+        for e in self.entries:
+            d = sd["tensors"].get(e.name)
+            if d is None:
+                continue
+            for k, v in e.state.items():
+                if k in d and d[k].numel() == v.numel():
+                    v.copy_(d[k])
+            for i, sst in enumerate(e.server_state):
+                for k, v in sst.items():
+                    key = f"server_{k}.{i}"
+                    if key in d and d[key].numel() == v.numel():
+                        v.copy_(d[key])
+
+    def stats(self) -> dict:
+        comp_elems = sum(e.numel for e in self.entries if e.compress and self.backend != "allreduce")
+        tot = sum(e.numel for e in self.entries)
+        return {"buckets": len(self.buckets), "fused_buckets": sum(b.fused for b in self.buckets),
+                "compressed_elems": comp_elems, "total_elems": tot, "backend": self.backend,
+                "kernel_launches": self.launch_count}
+
+    def close(self):
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None

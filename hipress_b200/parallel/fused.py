@@ -133,6 +133,30 @@ class FusedDenseBucket:
                                    _lib.stream_ptr(stream))
         _lib.check(rc, "fused dense launch")
 
+    def launch_ptrs(self, g_ptrs, r_ptrs, out_ptrs, sr_ptrs, *, step=0, salt=0, tensor_ids=None,
+                    stream=None):
+        """Same as :meth:`launch` from raw device addresses (one per tensor; None = absent)."""
+        L = _lib.cuda()
+        nseg = len(self.sizes)
+        cm = self._comm
+        for i in range(nseg):
+            s = self._segs[i]
+            s.g, s.r, s.out, s.sr = g_ptrs[i], r_ptrs[i], out_ptrs[i], sr_ptrs[i]
+            s.n = self.sizes[i]
+            s.id = tensor_ids[i] if tensor_ids is not None else i
+        self.epoch += 1
+        cm.nranks, cm.rank, cm.emulate = self.nranks, self.rank, 0
+        cm.epoch, cm.timeout_ns = self.epoch, self.timeout_ns
+        for q in range(self.nranks):
+            cm.inbox[q] = self.inbox_ptrs[q]
+            cm.flags[q] = self.flag_ptrs[q]
+        cm.status = self.status.data_ptr()
+        sp = self.spec
+        rc = L.hp_cuda_fused_dense(self.topo, sp.alg, sp.bits, self._segs, nseg, C.byref(cm),
+                                   sp.threshold, sp.seed, step, salt, self.ctas,
+                                   _lib.stream_ptr(stream))
+        _lib.check(rc, "fused dense launch")
+
     def check_status(self):
         """Synchronising read of the status words; raises on a recorded timeout."""
         words = self.status.cpu().tolist()

@@ -1,0 +1,70 @@
+"""Horovod-style ``DistributedOptimizer``: wraps any ``torch.optim`` optimizer so
+that ``step()`` first waits for the compressed synchronisation of all gradients.
+
+Reference parity: the reference front ends wrap the optimizer with Horovod's
+``DistributedOptimizer`` / ``DistributedTrainer`` plus an algorithm selector
+(``--algorithm tbq`` README.md:186, ``--comp-alg`` README.md:160 of
+mark14wu/hipress)."""
+from __future__ import annotations
+
+import torch
+
+from ..config import HipressConfig
+from .engine import GradSyncEngine
+
+
+class DistributedOptimizer:
+    def __init__(self, optimizer: torch.optim.Optimizer, named_parameters=None,
+                 config: HipressConfig | None = None, *, backward_passes_per_step: int = 1,
+                 group=None, **overrides):
+        """``overrides`` are :class:`HipressConfig` fields, e.g. ``algorithm="tbq"``,
+        ``topology="ring"``, ``comp_threshold=262144``, ``plan="SeCoPaPlan.txt"``."""
+        self.optimizer = optimizer
+        cfg = config or HipressConfig.from_env()
+        for k, v in overrides.items():
+            if not hasattr(cfg, k):
+                raise TypeError(f"unknown option {k}")
+            setattr(cfg, k, v)
+        if named_parameters is None:
+            named_parameters = [(f"param.{gi}.{pi}", p)
+                                for gi, g in enumerate(optimizer.param_groups)
+                                for pi, p in enumerate(g["params"])]
+        self.config = cfg
+        self.engine = GradSyncEngine(list(named_parameters), cfg, group=group,
+                                     backward_passes_per_step=backward_passes_per_step)
+        self._synchronized = False
+
+    # Horovod API
+    def synchronize(self):
+        self.engine.synchronize()
+        self._synchronized = True
+
+    def step(self, closure=None):
+        if not self._synchronized:
+            self.engine.synchronize()
+        self._synchronized = False
+        return self.optimizer.step(closure)
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.optimizer.zero_grad(set_to_none=set_to_none)
+
+    @property
+    def param_groups(self):
+        return self.optimizer.param_groups
+
+    def state_dict(self):
+        return {"optimizer": self.optimizer.state_dict(), "compressor_state": self.engine.state_dict()}
+
+    def load_state_dict(self, sd):
+        if "optimizer" in sd:
+            self.optimizer.load_state_dict(sd["optimizer"])
+            if sd.get("compressor_state"):
+                self.engine.load_state_dict(sd["compressor_state"])
+        else:
+            self.optimizer.load_state_dict(sd)
+
+    def close(self):
+        self.engine.close()
+
+    def __getattr__(self, name):
+        return getattr(self.__dict__["optimizer"], name)

@@ -50,11 +50,11 @@ def simulate_ring(comp: Compressor, grads, states, *, step=0, salt=0, tensor_id=
             st = _slice_state(states[r], lo, hi)
             inc = pay[(r - 1) % N][hop - 1] if hop > 0 else None
             if sp.sparse:
-                comp.update_state(g, st)
+                # merge first, then state update + selection in one encode
                 acc = st["accum_v"] if "accum_v" in st else st["residual"]
                 if inc is not None:
                     comp.decode(inc, acc, accumulate=True)
-                pay[r][hop] = comp.encode(g, st, update=False)
+                pay[r][hop] = comp.encode(g, st, update=True)
             else:
                 pay[r][hop] = comp.encode(g, st, incoming=inc, step=step,
                                           salt=salt + r * 256 + hop, tensor_id=tensor_id,
@@ -79,15 +79,13 @@ def simulate_ps(comp: Compressor, grads, states, server_states, *, step=0, salt=
     inv = 1.0 / N
     push = [[None] * N for _ in range(N)]  # push[src][owner]
     for r in range(N):
-        if sp.sparse:
-            comp.update_state(grads[r], states[r])
         for j in range(N):
             lo, hi = chunk_range(n, N, j)
             if hi <= lo:
                 continue
             st = _slice_state(states[r], lo, hi)
             if sp.sparse:
-                push[r][j] = comp.encode(grads[r][lo:hi], st, update=False)
+                push[r][j] = comp.encode(grads[r][lo:hi], st, update=True)
             else:
                 push[r][j] = comp.encode(grads[r][lo:hi], st, step=step, salt=salt + r * 256,
                                          tensor_id=tensor_id, elem_offset=lo)

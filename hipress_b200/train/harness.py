@@ -1,0 +1,104 @@
+"""Training harness shared by the launchers and the benchmark: builds one of the
+headline jobs (model, synthetic data of the named shape, optimizer wrapped in
+:class:`hipress_b200.DistributedOptimizer`) and exposes a ``step`` callable.
+
+Data is synthetic, as in the reference's benchmark runs ("synthetic data",
+README.md:153 of mark14wu/hipress): N(0,1) images with uniform random labels, or
+uniform random token ids with 15 % of positions masked."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from .. import DistributedOptimizer, HipressConfig, broadcast_parameters
+from ..models import get_model
+from ..parallel import comm
+
+# model -> (per-GPU batch, algorithm, topology) of the headline configurations
+HEADLINE = {
+    "vgg19": dict(batch=32, algorithm="tbq", topology="ring"),
+    "resnet50": dict(batch=128, algorithm="dgc", topology="ps"),
+    "bert_large": dict(batch=32, algorithm="onebit", topology="ring"),
+}
+
+
+@dataclass
+class Job:
+    model: torch.nn.Module
+    optimizer: DistributedOptimizer
+    kind: str           # "image" | "mlm"
+    batch: int
+    seq_len: int
+    device: torch.device
+    dtype: torch.dtype
+
+    # ---------------------------------------------------------------- data
+    def host_batch(self, seed: int):
+        """One synthetic batch in pinned host memory."""
+        g = torch.Generator().manual_seed(seed)
+        if self.kind == "image":
+            x = torch.randn(self.batch, 3, 224, 224, generator=g)
+            y = torch.randint(0, 1000, (self.batch,), generator=g)
+        else:
+            V = self.model.c.vocab_size
+            x = torch.randint(0, V, (self.batch, self.seq_len), generator=g)
+            y = torch.full((self.batch, self.seq_len), -100, dtype=torch.long)
+            mask = torch.rand(self.batch, self.seq_len, generator=g) < 0.15
+            mask[:, 0] |= ~mask.any(dim=1)  # at least one masked position per sample
+            y[mask] = x[mask]
+            x = x.clone()
+            x[mask] = 103  # [MASK]
+        if self.device.type == "cuda":
+            x, y = x.pin_memory(), y.pin_memory()
+        return x, y
+
+    def to_device(self, x, y):
+        x = x.to(self.device, non_blocking=True)
+        y = y.to(self.device, non_blocking=True)
+        if self.kind == "image" and self.device.type == "cuda":
+            x = x.contiguous(memory_format=torch.channels_last)
+        return x, y
+
+    def h2d_bytes(self, x, y):
+        return x.numel() * x.element_size() + y.numel() * y.element_size()
+
+    # ---------------------------------------------------------------- step
+    def step(self, x, y):
+        """Forward, backward (compressed synchronisation overlaps it), update.
+        Returns the loss as a device tensor."""
+        self.optimizer.zero_grad(set_to_none=True)
+        with torch.autocast(self.device.type, dtype=self.dtype,
+                            enabled=self.dtype != torch.float32):
+            if self.kind == "image":
+                loss = F.cross_entropy(self.model(x).float(), y)
+            else:
+                loss = self.model(x, y)
+        loss.backward()
+        self.optimizer.step()
+        return loss.detach()
+
+
+def build_job(model_name: str = "vgg19", config: HipressConfig | None = None, *, batch=None,
+              seq_len: int = 128, dtype=torch.bfloat16, lr: float = 0.01, device=None,
+              model_kwargs=None, seed: int = 0) -> Job:
+    if not comm.is_initialized():
+        comm.init()
+    name = model_name.lower().replace("-", "_")
+    head = HEADLINE.get(name, HEADLINE["vgg19"])
+    cfg = config or HipressConfig.from_env(algorithm=head["algorithm"], topology=head["topology"])
+    device = device or comm.device()
+    torch.manual_seed(seed)  # same initial weights on every rank
+    model = get_model(name, **(model_kwargs or {})).to(device)
+    kind = "mlm" if name.startswith("bert") else "image"
+    if kind == "image" and device.type == "cuda":
+        model = model.to(memory_format=torch.channels_last)
+    model.train()
+    named = list(model.gluon_named_parameters()) if hasattr(model, "gluon_named_parameters") \
+        else list(model.named_parameters())
+    inner = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9,
+                            **({"fused": True} if device.type == "cuda" else {}))
+    opt = DistributedOptimizer(inner, named, cfg)
+    broadcast_parameters(model.state_dict(), root_rank=0)
+    return Job(model, opt, kind, batch or head["batch"], seq_len, device, dtype)

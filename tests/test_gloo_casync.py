@@ -1,0 +1,147 @@
+"""Multi-process CPU tests (gloo, world_size 2 and 3): the CaSync host schedule
+against the lock-step simulation, and the headline CPU configuration: TBQ
+(threshold 0.01) + error feedback, CaSync-Ring, comp-threshold 1024, MLP
+784->256->10 gradients ~ N(0, 1e-3), 10 steps against uncompressed all-reduce."""
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from hipress_b200.ops import Compressor
+from hipress_b200.parallel.simulate import chunk_elems, simulate_ps, simulate_ring
+
+SHAPES = [(256, 784), (256,), (10, 256), (10,)]
+
+
+def _spawn(fn, world, *args):
+    from _mp import spawn
+    return spawn(fn, world, *args, backend="gloo")
+
+
+def _grads(rank, step):
+    g = torch.Generator().manual_seed(1000 * step + rank)
+    return [torch.randn(s, generator=g) * 1e-3 for s in SHAPES]
+
+
+# ----------------------------------------------------------------------------
+def _run_optimizer(rank, world, alg, topo, steps):
+    import hipress_b200 as hp
+    params = [torch.nn.Parameter(torch.zeros(s)) for s in SHAPES]
+    names = ["fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
+    opt = hp.DistributedOptimizer(torch.optim.SGD(params, lr=1.0), list(zip(names, params)),
+                                  algorithm=alg, topology=topo, comp_threshold=1024,
+                                  threshold=0.01, ratio=0.01)
+    outs = []
+    for step in range(steps):
+        for p, g in zip(params, _grads(rank, step)):
+            p.grad = g.clone()
+        opt.synchronize()
+        outs.append([p.grad.clone() for p in params])
+        opt._synchronized = False
+    state = opt.state_dict()["compressor_state"]
+    return {"outs": outs, "state": state, "stats": opt.engine.stats()}
+
+
+def _simulate(world, alg, topo, steps, **kw):
+    comp = Compressor(alg, threshold=0.01, ratio=0.01)
+    big = [i for i, s in enumerate(SHAPES) if torch.Size(s).numel() >= 1024]
+    states = {i: [comp.new_state(torch.Size(SHAPES[i]).numel(), "cpu") for _ in range(world)] for i in big}
+    sst = {i: [({"residual": torch.zeros(chunk_elems(torch.Size(SHAPES[i]).numel(), world))}
+                if (comp.spec.sparse or "residual" in comp.spec.state_names()) else {})
+               for _ in range(world)] for i in big}
+    outs = []
+    for step in range(steps):
+        gs = [_grads(r, step) for r in range(world)]
+        row = []
+        for i, s in enumerate(SHAPES):
+            if i in big:
+                flat = [gs[r][i].reshape(-1).clone() for r in range(world)]
+                if topo == "ring":
+                    res = simulate_ring(comp, flat, states[i], step=step, tensor_id=i * 64)
+                else:
+                    res = simulate_ps(comp, flat, states[i], sst[i], step=step, tensor_id=i * 64)
+                row.append(res[0].view(s))
+            else:
+                row.append(sum(gs[r][i] for r in range(world)) / world)
+        outs.append(row)
+    return outs, states
+
+
+@pytest.mark.parametrize("alg,topo,world", [("tbq", "ring", 2), ("tbq", "ps", 3), ("onebit", "ring", 3),
+                                            ("terngrad", "ps", 2), ("dgc", "ps", 2),
+                                            ("graddrop", "ring", 2), ("dgc", "ring", 3)])
+def test_host_schedule_matches_simulation(alg, topo, world):
+    steps = 3
+    res = _spawn(_run_optimizer, world, alg, topo, steps)
+    ref, states = _simulate(world, alg, topo, steps)
+    for r in range(world):
+        for step in range(steps):
+            for i in range(len(SHAPES)):
+                got, want = res[r]["outs"][step][i], ref[step][i]
+                assert torch.allclose(got, want, rtol=1e-6, atol=1e-9), (alg, topo, r, step, i)
+        # every rank holds the same averaged gradient
+        for step in range(steps):
+            for i in range(len(SHAPES)):
+                assert torch.equal(res[r]["outs"][step][i], res[0]["outs"][step][i])
+    assert res[0]["stats"]["compressed_elems"] == 256 * 784 + 10 * 256
+
+
+def test_config1_tbq_ring_tracks_uncompressed_allreduce():
+    """10 steps: delivered + pending residual == exact average, and what was
+    delivered is a sum of +-threshold levels divided by N."""
+    world, steps = 2, 10
+    res = _spawn(_run_optimizer, world, "tbq", "ring", steps)
+    exact = [sum(_grads(r, s)[0] for r in range(world)) / world for s in range(steps)]
+    delivered = sum(res[0]["outs"][s][0] for s in range(steps))
+    pending = sum(res[r]["state"]["tensors"]["fc1.weight"]["residual"] for r in range(world)) / world
+    total = sum(exact)
+    assert torch.allclose(delivered.reshape(-1) + pending, total.reshape(-1), atol=1e-6)
+    # small tensors are averaged exactly
+    for s in range(steps):
+        want = sum(_grads(r, s)[1] for r in range(world)) / world
+        assert torch.allclose(res[0]["outs"][s][1], want, atol=1e-8)
+    lv = (delivered / 0.005).round()
+    assert torch.allclose(delivered, lv * 0.005, atol=1e-6)
+
+
+def _run_uncompressed(rank, world, steps):
+    import hipress_b200 as hp
+    params = [torch.nn.Parameter(torch.zeros(s)) for s in SHAPES]
+    opt = hp.DistributedOptimizer(torch.optim.SGD(params, lr=1.0), None, algorithm="none")
+    outs = []
+    for step in range(steps):
+        for p, g in zip(params, _grads(rank, step)):
+            p.grad = g.clone()
+        opt.step()
+        outs.append([p.detach().clone() for p in params])
+    return outs
+
+
+def test_uncompressed_path_is_exact_average():
+    res = _spawn(_run_uncompressed, 2, 2)
+    acc = [torch.zeros(s) for s in SHAPES]
+    for step in range(2):
+        for i in range(len(SHAPES)):
+            acc[i] -= sum(_grads(r, step)[i] for r in range(2)) / 2
+            assert torch.allclose(res[0][step][i], acc[i], atol=1e-7)
+            assert torch.equal(res[0][step][i], res[1][step][i])
+
+
+def _run_mismatch(rank, world):
+    import hipress_b200 as hp
+    shapes = SHAPES if rank == 0 else SHAPES[:-1]
+    params = [torch.nn.Parameter(torch.zeros(s)) for s in shapes]
+    try:
+        hp.DistributedOptimizer(torch.optim.SGD(params, lr=1.0), None, algorithm="tbq")
+        return "no error"
+    except RuntimeError as e:
+        return str(e)
+
+
+def test_parameter_order_mismatch_is_detected():
+    res = _spawn(_run_mismatch, 2)
+    assert all("disagree" in r for r in res)
