@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--comprplan", default=None)
     ap.add_argument("--sync-backend", default="auto", choices=["auto", "fused", "host", "allreduce"])
     ap.add_argument("--ctas", type=int, default=None)
+    ap.add_argument("--partition-sms", type=int, default=None)
+    ap.add_argument("--partition-ctas", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -127,6 +129,10 @@ def main():
                 comp_threshold=a.comp_threshold, plan=a.comprplan, backend=a.sync_backend)
     if a.ctas:
         over["ctas"] = a.ctas
+    if a.partition_sms is not None:
+        over["partition_sms"] = a.partition_sms
+    if a.partition_ctas:
+        over["partition_ctas"] = a.partition_ctas
     cfg = hp.HipressConfig.from_env(**over)
     job = build_job(a.model, cfg, batch=a.batch, seq_len=a.seq_len)
     eng = job.optimizer.engine
@@ -201,7 +207,8 @@ def main():
                        "comp_threshold": cfg.comp_threshold, "sync_backend": eng.backend,
                        "gradients": "fp32", "compressed_fraction":
                            round(st["compressed_elems"] / st["total_elems"], 4),
-                       "buckets": st["buckets"],
+                       "buckets": st["buckets"], "ctas": cfg.ctas, "partition_sms": cfg.partition_sms,
+                       "partition_ctas": cfg.partition_ctas,
                        "l2": "inputs larger than L2: weights+gradients+activations of one step "
                              "exceed the 126 MB L2 many times; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": float(loss.item()),

@@ -163,11 +163,11 @@ __device__ __forceinline__ void decode_frag(uint32_t frag, const float (&meta)[2
 // Quantise the register tile x (m valid elements).  On return frag[] holds the
 // code fragments (zero for elements past m), meta[] the tile metadata, and x the
 // quantisation error x - decode(code) of every valid element.
-template <int ALG, int B>
-__device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const DenseParams& P,
-                                            uint32_t tensor_id, uint64_t elem0, uint32_t salt,
-                                            TileSmem& s, float (&meta)[2],
-                                            uint32_t (&frag)[kIter]) {
+template <int ALG, int B, bool FULL>
+__device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, const DenseParams& P,
+                                                 uint32_t tensor_id, uint64_t elem0, uint32_t salt,
+                                                 TileSmem& s, float (&meta)[2],
+                                                 uint32_t (&frag)[kIter]) {
   meta[0] = 0.0f;
   meta[1] = 0.0f;
   if (ALG == kOnebit) {
@@ -176,7 +176,7 @@ __device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const D
     for (int j = 0; j < kIter; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        if (4 * (j * kThreads + (int)threadIdx.x) + e < m) part += (double)fabsf(x[j][e]);
+        if (FULL || 4 * (j * kThreads + (int)threadIdx.x) + e < m) part += (double)fabsf(x[j][e]);
     const double tot = block_sum(part, s);
     meta[0] = (float)(tot / (double)m);
   } else if (ALG == kTernGrad) {
@@ -185,7 +185,7 @@ __device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const D
     for (int j = 0; j < kIter; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        if (4 * (j * kThreads + (int)threadIdx.x) + e < m) {
+        if (FULL || 4 * (j * kThreads + (int)threadIdx.x) + e < m) {
           mn = fminf(mn, x[j][e]);
           mx = fmaxf(mx, x[j][e]);
         }
@@ -206,7 +206,7 @@ __device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const D
     uint32_t f = 0u;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      if (i0 + e < m) {
+      if (FULL || i0 + e < m) {
         uint32_t c;
         float d;
         if (ALG == kOnebit) {
@@ -225,6 +225,15 @@ __device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const D
     }
     frag[j] = f;
   }
+}
+
+template <int ALG, int B>
+__device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const DenseParams& P,
+                                            uint32_t tensor_id, uint64_t elem0, uint32_t salt,
+                                            TileSmem& s, float (&meta)[2],
+                                            uint32_t (&frag)[kIter]) {
+  if (m == kTile) encode_tile_impl<ALG, B, true>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
+  else encode_tile_impl<ALG, B, false>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
 }
 
 // Byte layout of one dense payload of `n_layout` elements (n_layout fixes where

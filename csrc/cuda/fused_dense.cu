@@ -26,6 +26,7 @@
 
 #include "dense_tile.cuh"
 #include "hipress/capi.h"
+#include "pipeline.cuh"
 #include "sync.cuh"
 
 namespace hipress {
@@ -38,7 +39,7 @@ struct SegDev {
   uint32_t n;
   uint32_t chunk;        // elements per chunk, multiple of kTile
   uint32_t tiles;        // tiles per chunk
-  uint32_t tile_prefix;  // tiles of the segments before this one
+  uint32_t tile_prefix;  // super-tiles (groups of kSuper tiles) of the segments before this one
   uint32_t pay_off;      // byte offset of this segment's chunk payload inside a slot
   uint32_t id;
 };
@@ -46,20 +47,18 @@ struct SegDev {
 struct BucketDev {
   SegDev seg[HP_MAX_SEGS];
   int nseg;
-  uint32_t tiles_total;  // tiles of one chunk summed over segments
+  uint32_t tiles_total;  // super-tiles of one chunk summed over segments
   uint64_t slot_bytes;
 };
+
+// CTAs take work in groups of kSuper consecutive tiles so that the per-group
+// bookkeeping (which tensor, where, how many valid elements) is paid once.
+constexpr int kSuper = 4;
 
 struct FusedParams {
   DenseParams P;
   float inv_n;
 };
-
-__device__ __forceinline__ int find_seg(const BucketDev& bk, uint32_t tt) {
-  int i = bk.nseg - 1;
-  while (i > 0 && tt < bk.seg[i].tile_prefix) --i;
-  return i;
-}
 
 // decode tile t of the payload at `base` and add it to x (or assign when !add)
 template <int ALG, int B>
@@ -102,117 +101,360 @@ __device__ __forceinline__ uint32_t chunk_valid(uint32_t n, uint32_t chunk, int 
   return (uint32_t)(rest < chunk ? rest : chunk);
 }
 
-// ------------------------------------------------------------------------ ring
-template <int ALG, int B>
-__global__ void __launch_bounds__(kThreads)
-ring_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
-  __shared__ TileSmem s;
-  __shared__ WaitState ws;
+// ------------------------------------------------------------ shared memory
+constexpr int kStages = 3;  // tiles of g (+ r) in flight per CTA
+
+struct FusedSmem {
+  alignas(128) float g[kStages][kTile];
+  alignas(128) float r[kStages][kTile];
+  TileSmem tile;
+  alignas(8) uint64_t full[kStages];
+  WaitState ws;
+};
+
+// ------------------------------------------------ encode phases (ring hops / PS push)
+// What one phase of the encode sequence does, as a function of topology.
+struct PhaseSpec {
+  int chunk;      // chunk of every tensor handled in this phase
+  int in_slot;    // inbox slot to wait for and merge, or -1
+  int ndst;       // payload goes to ranks (dst0 + q) % N, q < ndst
+  int dst0;
+  int dst_slot;   // slot index inside the destination inbox (and flag row)
+  uint32_t salt;
+};
+
+template <int TOPO>
+__device__ __forceinline__ PhaseSpec phase_spec(int ph, int N, int R) {
+  PhaseSpec p;
+  if (TOPO == HP_TOPO_RING) {
+    p.chunk = (R - ph + N) % N;
+    p.in_slot = ph > 0 ? ph - 1 : -1;
+    if (ph < N - 1) {
+      p.ndst = 1; p.dst0 = (R + 1) % N; p.dst_slot = ph;
+    } else {
+      p.ndst = N; p.dst0 = R; p.dst_slot = N - 1 + R;
+    }
+    p.salt = (uint32_t)(R * 256 + ph);
+  } else {  // PS push: remote owners first, own chunk last
+    p.chunk = (R + 1 + ph) % N;
+    p.in_slot = -1;
+    p.ndst = 1; p.dst0 = p.chunk; p.dst_slot = R;
+    p.salt = (uint32_t)(R * 256);
+  }
+  return p;
+}
+
+struct TileRef {
+  int seg;
+  uint32_t t0, cnt, nv;  // tiles t0 .. t0+cnt-1 of (seg, chunk); nv valid elements in the chunk
+  size_t off0;           // element offset of tile t0 inside the tensor
+};
+
+// Walks the super-tiles of one phase that belong to this CTA: super-tile
+// (tile_prefix + st) of the bucket goes to CTA (tile_prefix + st) % G.
+struct Cursor {
+  int phase, seg, chunk;
+  uint32_t st, nvt, nv;  // next super-tile, valid tiles and valid elements of (seg, chunk)
+};
+
+__device__ __forceinline__ void cursor_enter_seg(const BucketDev& bk, int G, int b, Cursor& c) {
+  if (c.seg >= bk.nseg) return;
+  const SegDev& sg = bk.seg[c.seg];
+  c.nv = chunk_valid(sg.n, sg.chunk, c.chunk);
+  c.nvt = (c.nv + kTile - 1) / kTile;
+  const uint32_t p = sg.tile_prefix % (uint32_t)G;
+  c.st = ((uint32_t)b + (uint32_t)G - p) % (uint32_t)G;
+}
+
+__device__ __forceinline__ void cursor_begin(const BucketDev& bk, int G, int b, int phase,
+                                             int chunk, Cursor& c) {
+  c.phase = phase;
+  c.chunk = chunk;
+  c.seg = 0;
+  cursor_enter_seg(bk, G, b, c);
+}
+
+// next super-tile of the cursor's phase; false when the phase is exhausted
+__device__ __forceinline__ bool cursor_next(const BucketDev& bk, int G, int b, Cursor& c,
+                                            TileRef& out) {
+  while (c.seg < bk.nseg) {
+    const uint32_t t0 = c.st * kSuper;
+    if (t0 < c.nvt) {
+      const SegDev& sg = bk.seg[c.seg];
+      const uint32_t rest = c.nvt - t0;
+      out.seg = c.seg;
+      out.t0 = t0;
+      out.cnt = rest < (uint32_t)kSuper ? rest : (uint32_t)kSuper;
+      out.nv = c.nv;
+      out.off0 = (size_t)c.chunk * sg.chunk + (size_t)t0 * kTile;
+      c.st += (uint32_t)G;
+      return true;
+    }
+    ++c.seg;
+    cursor_enter_seg(bk, G, b, c);
+  }
+  return false;
+}
+
+__device__ __forceinline__ int tile_valid(const TileRef& tr, uint32_t u) {
+  const uint32_t left = tr.nv - (tr.t0 + u) * kTile;
+  return (int)(left < (uint32_t)kTile ? left : (uint32_t)kTile);
+}
+
+// a tile can be prefetched with a bulk copy when it is full and 16-byte aligned
+__device__ __forceinline__ bool bulk_ok(const float* g, const float* r, int m) {
+  return m == kTile && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(r)) & 15) == 0;
+}
+
+__device__ __forceinline__ void load_tile_smem(const float* sp, float (&x)[kIter][4]) {
+#pragma unroll
+  for (int j = 0; j < kIter; ++j) {
+    const float4 v = *reinterpret_cast<const float4*>(sp + 4 * (j * kThreads + (int)threadIdx.x));
+    x[j][0] = v.x; x[j][1] = v.y; x[j][2] = v.z; x[j][3] = v.w;
+  }
+}
+
+template <int ALG, int B, int TOPO>
+__device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm& cm,
+                                              const FusedParams& fp, FusedSmem& sm, int R, int E,
+                                              uint32_t* status) {
   const int N = cm.nranks;
-  const int R = cm.emulate ? (int)blockIdx.y : cm.rank;
-  const int E = cm.emulate ? (int)blockIdx.y : 0;
   const int G = (int)gridDim.x;
   const int b = (int)blockIdx.x;
-  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   uint8_t* my_inbox = reinterpret_cast<uint8_t*>(cm.inbox[R]);
   uint32_t* my_flags = reinterpret_cast<uint32_t*>(cm.flags[R]);
-  wait_init(ws);
+  // prefetcher state: runs ahead of the consumer over the same tile sequence
+  Cursor prod;
+  cursor_begin(bk, G, b, 0, phase_spec<TOPO>(0, N, R).chunk, prod);
+  TileRef pr;
+  pr.cnt = 0;
+  uint32_t pu = 0;           // next tile inside pr
+  const float* pg = nullptr; // g / r addresses of tile pu of pr
+  const float* prr = nullptr;
+  bool prod_more = true;
+  uint32_t issued = 0, consumed = 0;  // tiles prefetched / used through the bulk pipeline
 
-  for (int hop = 0; hop < N; ++hop) {
-    const int c = (R - hop + N) % N;
-    const bool last = hop == N - 1;
-    if (hop > 0)
-      wait_flag(my_flags + (size_t)(hop - 1) * G + b, cm.epoch, cm.timeout_ns, status,
-                HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)(hop - 1) << 8) | (b & 255), ws);
-    const uint8_t* in_slot = my_inbox + (size_t)(hop > 0 ? hop - 1 : 0) * bk.slot_bytes;
-    const int succ = (R + 1) % N;
-    for (uint32_t tt = b; tt < bk.tiles_total; tt += G) {
-      const SegDev& sg = bk.seg[find_seg(bk, tt)];
-      const uint32_t t = tt - sg.tile_prefix;
-      const uint32_t nv = chunk_valid(sg.n, sg.chunk, c);
-      const int64_t left = (int64_t)nv - (int64_t)t * kTile;
-      if (left <= 0) continue;
-      const int m = (int)(left < kTile ? left : kTile);
-      const size_t off = (size_t)c * sg.chunk + (size_t)t * kTile;
-      float x[kIter][4];
-      load_tile(sg.g + E * cm.emu_stride_g + off, m, x);
-      if (hop > 0) decode_into<ALG, B>(in_slot + sg.pay_off, sg.chunk, t, m, fp.P.tau, true, x);
-      float* rp = sg.r ? sg.r + E * cm.emu_stride_r + off : nullptr;
-      if (rp) {
-        float rr[kIter][4];
-        load_tile(rp, m, rr);
+  for (int ph = 0; ph < N; ++ph) {
+    const PhaseSpec ps = phase_spec<TOPO>(ph, N, R);
+    Cursor cons;
+    cursor_begin(bk, G, b, ph, ps.chunk, cons);
+    uint8_t* dst_base[HP_MAX_RANKS];
 #pragma unroll
-        for (int j = 0; j < kIter; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) x[j][e] = rr[j][e] + x[j][e];
-      }
-      float meta[2];
-      uint32_t frag[kIter];
-      encode_tile<ALG, B>(x, m, fp.P, sg.id, off, fp.P.salt + (uint32_t)(R * 256 + hop), s, meta,
-                          frag);
-      if (rp) store_tile(rp, m, x);
-      stage_frags<B>(s.codes, frag);
-      __syncthreads();
-      if (!last) {
-        uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[succ]) + (size_t)hop * bk.slot_bytes +
-                       sg.pay_off;
-        store_payload_tile<ALG, B>(dst, sg.chunk, t, m, nv, meta, fp.P.tau, s);
-      } else {
-        for (int q = 0; q < N; ++q) {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) +
-                         (size_t)(N - 1 + R) * bk.slot_bytes + sg.pay_off;
-          store_payload_tile<ALG, B>(dst, sg.chunk, t, m, nv, meta, fp.P.tau, s);
+    for (int q = 0; q < HP_MAX_RANKS; ++q)
+      dst_base[q] = q < ps.ndst ? reinterpret_cast<uint8_t*>(cm.inbox[(ps.dst0 + q) % N]) +
+                                      (size_t)ps.dst_slot * bk.slot_bytes
+                                : nullptr;
+    const uint8_t* in_base =
+        ps.in_slot >= 0 ? my_inbox + (size_t)ps.in_slot * bk.slot_bytes : nullptr;
+    bool waited = ps.in_slot < 0;
+    TileRef tr;
+    while (cursor_next(bk, G, b, cons, tr)) {
+      const SegDev& sg = bk.seg[tr.seg];
+      const float* gp0 = sg.g + E * cm.emu_stride_g + tr.off0;
+      float* rp0 = sg.r ? sg.r + E * cm.emu_stride_r + tr.off0 : nullptr;
+      const bool aligned =
+          ((reinterpret_cast<uintptr_t>(gp0) | reinterpret_cast<uintptr_t>(rp0)) & 15) == 0;
+      for (uint32_t u = 0; u < tr.cnt; ++u) {
+        // top up the prefetch pipeline (stages of finished tiles are free: the
+        // previous tile ended with a CTA barrier)
+        while (prod_more && issued - consumed < kStages) {
+          if (pu >= pr.cnt) {
+            bool got = cursor_next(bk, G, b, prod, pr);
+            while (!got && prod.phase + 1 < N) {  // run ahead across phases
+              cursor_begin(bk, G, b, prod.phase + 1,
+                           phase_spec<TOPO>(prod.phase + 1, N, R).chunk, prod);
+              got = cursor_next(bk, G, b, prod, pr);
+            }
+            if (!got) {
+              prod_more = false;
+              break;
+            }
+            const SegDev& psg = bk.seg[pr.seg];
+            pg = psg.g + E * cm.emu_stride_g + pr.off0;
+            prr = psg.r ? psg.r + E * cm.emu_stride_r + pr.off0 : nullptr;
+            pu = 0;
+          }
+          if (bulk_ok(pg, prr, tile_valid(pr, pu))) {
+            if (threadIdx.x == 0) {
+              const int st = issued % kStages;
+              mbar_expect_tx(&sm.full[st], (prr ? 2u : 1u) * kTile * 4u);
+              bulk_load(sm.g[st], pg, kTile * 4u, &sm.full[st]);
+              if (prr) bulk_load(sm.r[st], prr, kTile * 4u, &sm.full[st]);
+            }
+            ++issued;
+          }
+          ++pu;
+          pg += kTile;
+          if (prr) prr += kTile;
         }
+        if (!waited) {  // the incoming payload is needed only now; g and r are already in flight
+          wait_flag(my_flags + (size_t)ps.in_slot * G + b, cm.epoch, cm.timeout_ns, status,
+                    HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
+                    sm.ws);
+          waited = true;
+        }
+        const int m = tile_valid(tr, u);
+        const uint32_t t = tr.t0 + u;
+        const float* gp = gp0 + (size_t)u * kTile;
+        float* rp = rp0 ? rp0 + (size_t)u * kTile : nullptr;
+        float x[kIter][4];
+        // loads of the incoming payload go out before anything waits
+        uint32_t ifr[kIter];
+        float imeta[2];
+        if (in_base) {
+          PayloadView iv = payload_view(const_cast<uint8_t*>(in_base + sg.pay_off), ALG, sg.chunk);
+          load_meta<ALG>(iv.meta, t, imeta);
+          const uint8_t* tc = iv.codes + (size_t)t * (kTile * B / 8);
+#pragma unroll
+          for (int j = 0; j < kIter; ++j) ifr[j] = load_frag<B>(tc, j, m);
+        }
+        const bool bulk = aligned && m == kTile;
+        int st = 0;
+        if (bulk) {
+          st = consumed % kStages;
+          if (!sm.ws.poisoned &&
+              !mbar_wait_bounded(&sm.full[st], (consumed / kStages) & 1, cm.timeout_ns, status,
+                                 HP_STATUS_TIMEOUT | (3u << 16) | (b & 255)))
+            sm.ws.poisoned = 1;
+          ++consumed;
+          load_tile_smem(sm.g[st], x);
+        } else {
+          load_tile(gp, m, x);
+        }
+        if (in_base) {
+#pragma unroll
+          for (int j = 0; j < kIter; ++j) {
+            float d[4];
+            decode_frag<ALG, B>(ifr[j], imeta, fp.P.tau, d);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] + d[e];
+          }
+        }
+        if (rp) {
+          float rr[kIter][4];
+          if (bulk) load_tile_smem(sm.r[st], rr);
+          else load_tile(rp, m, rr);
+#pragma unroll
+          for (int j = 0; j < kIter; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[j][e] = rr[j][e] + x[j][e];
+        }
+        float meta[2];
+        uint32_t frag[kIter];
+        encode_tile<ALG, B>(x, m, fp.P, sg.id, tr.off0 + (size_t)u * kTile, fp.P.salt + ps.salt,
+                            sm.tile, meta, frag);
+        if (rp) store_tile(rp, m, x);
+        stage_frags<B>(sm.tile.codes, frag);
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < HP_MAX_RANKS; ++q)
+          if (q < ps.ndst)
+            store_payload_tile<ALG, B>(dst_base[q] + sg.pay_off, sg.chunk, t, m, tr.nv, meta,
+                                       fp.P.tau, sm.tile);
+        __syncthreads();
       }
-      __syncthreads();
     }
-    // publish: everything this CTA stored for this hop is complete
+    if (!waited)  // no tile in this phase, the flag protocol still runs
+      wait_flag(my_flags + (size_t)ps.in_slot * G + b, cm.epoch, cm.timeout_ns, status,
+                HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255), sm.ws);
+    // publish: everything this CTA stored for this phase is complete
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence_system();
-      if (!last) {
-        st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[succ]) + (size_t)hop * G + b, cm.epoch);
-      } else {
-        for (int q = 0; q < N; ++q)
-          st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + q) % N]) +
-                             (size_t)(N - 1 + R) * G + b,
-                         cm.epoch);
+      for (int q = 0; q < ps.ndst; ++q)
+        st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(ps.dst0 + q) % N]) +
+                           (size_t)ps.dst_slot * G + b,
+                       cm.epoch);
+    }
+  }
+}
+
+// decode the reduced chunk `c` that arrived in inbox slot `slot` into the gradient
+template <int ALG, int B>
+__device__ __forceinline__ void decode_phase(const BucketDev& bk, const HpComm& cm,
+                                             const FusedParams& fp, FusedSmem& sm, int R, int E,
+                                             int slot, int c, uint32_t* status) {
+  const int G = (int)gridDim.x;
+  const int b = (int)blockIdx.x;
+  uint8_t* my_inbox = reinterpret_cast<uint8_t*>(cm.inbox[R]);
+  uint32_t* my_flags = reinterpret_cast<uint32_t*>(cm.flags[R]);
+  wait_flag(my_flags + (size_t)slot * G + b, cm.epoch, cm.timeout_ns, status,
+            HP_STATUS_TIMEOUT | (2u << 16) | ((uint32_t)slot << 8) | (b & 255), sm.ws);
+  const uint8_t* sp = my_inbox + (size_t)slot * bk.slot_bytes;
+  Cursor cur;
+  cursor_begin(bk, G, b, 0, c, cur);
+  TileRef tr;
+  while (cursor_next(bk, G, b, cur, tr)) {
+    const SegDev& sg = bk.seg[tr.seg];
+    float* op = sg.out + E * cm.emu_stride_out + tr.off0;
+    PayloadView v = payload_view(const_cast<uint8_t*>(sp + sg.pay_off), ALG, sg.chunk);
+    // issue every payload load of the super-tile first, then decode and store:
+    // one exposed L2 round trip per kSuper tiles instead of one per tile
+    uint32_t fr[kSuper][kIter];
+    float mt[kSuper][2];
+#pragma unroll
+    for (uint32_t u = 0; u < (uint32_t)kSuper; ++u) {
+      if (u < tr.cnt) {
+        const int m = tile_valid(tr, u);
+        load_meta<ALG>(v.meta, tr.t0 + u, mt[u]);
+        const uint8_t* tc = v.codes + (size_t)(tr.t0 + u) * (kTile * B / 8);
+#pragma unroll
+        for (int j = 0; j < kIter; ++j) fr[u][j] = load_frag<B>(tc, j, m);
+      }
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < (uint32_t)kSuper; ++u) {
+      if (u < tr.cnt) {
+        const int m = tile_valid(tr, u);
+        float x[kIter][4];
+#pragma unroll
+        for (int j = 0; j < kIter; ++j) {
+          float d[4];
+          decode_frag<ALG, B>(fr[u][j], mt[u], fp.P.tau, d);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[j][e] = d[e] * fp.inv_n;
+        }
+        store_tile(op + (size_t)u * kTile, m, x);
       }
     }
   }
+}
 
-  // gather: decode the N reduced chunks (rank src finalised chunk src+1)
+__device__ __forceinline__ void fused_prologue(FusedSmem& sm) {
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) mbar_init(&sm.full[i], 1);
+    mbar_init_fence();
+    sm.ws.poisoned = 0;
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------ ring
+template <int ALG, int B>
+__global__ void __launch_bounds__(kThreads, 2)
+ring_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
+  const int N = cm.nranks;
+  const int R = cm.emulate ? (int)blockIdx.y : cm.rank;
+  const int E = cm.emulate ? (int)blockIdx.y : 0;
+  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
+  fused_prologue(sm);
+  encode_phases<ALG, B, HP_TOPO_RING>(bk, cm, fp, sm, R, E, status);
+  // gather: rank src finalised chunk src+1
   for (int qq = 0; qq < N; ++qq) {
     const int src = (R + qq) % N;
-    const int c = (src + 1) % N;
-    wait_flag(my_flags + (size_t)(N - 1 + src) * G + b, cm.epoch, cm.timeout_ns, status,
-              HP_STATUS_TIMEOUT | (2u << 16) | ((uint32_t)src << 8) | (b & 255), ws);
-    const uint8_t* slot = my_inbox + (size_t)(N - 1 + src) * bk.slot_bytes;
-    for (uint32_t tt = b; tt < bk.tiles_total; tt += G) {
-      const SegDev& sg = bk.seg[find_seg(bk, tt)];
-      const uint32_t t = tt - sg.tile_prefix;
-      const uint32_t nv = chunk_valid(sg.n, sg.chunk, c);
-      const int64_t left = (int64_t)nv - (int64_t)t * kTile;
-      if (left <= 0) continue;
-      const int m = (int)(left < kTile ? left : kTile);
-      const size_t off = (size_t)c * sg.chunk + (size_t)t * kTile;
-      float x[kIter][4];
-      decode_into<ALG, B>(slot + sg.pay_off, sg.chunk, t, m, fp.P.tau, false, x);
-#pragma unroll
-      for (int j = 0; j < kIter; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] * fp.inv_n;
-      store_tile(sg.out + E * cm.emu_stride_out + off, m, x);
-    }
+    decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N - 1 + src, (src + 1) % N, status);
   }
 }
 
 // -------------------------------------------------------------------------- PS
 template <int ALG, int B>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
-  __shared__ TileSmem s;
-  __shared__ WaitState ws;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
+  TileSmem& s = sm.tile;
   const int N = cm.nranks;
   const int R = cm.emulate ? (int)blockIdx.y : cm.rank;
   const int E = cm.emulate ? (int)blockIdx.y : 0;
@@ -221,85 +463,53 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   uint8_t* my_inbox = reinterpret_cast<uint8_t*>(cm.inbox[R]);
   uint32_t* my_flags = reinterpret_cast<uint32_t*>(cm.flags[R]);
-  wait_init(ws);
+  fused_prologue(sm);
 
-  // phase 1: push.  Remote owners first, own chunk last.
-  for (int i = 0; i < N; ++i) {
-    const int j = (R + 1 + i) % N;
-    uint8_t* dslot = reinterpret_cast<uint8_t*>(cm.inbox[j]) + (size_t)R * bk.slot_bytes;
-    for (uint32_t tt = b; tt < bk.tiles_total; tt += G) {
-      const SegDev& sg = bk.seg[find_seg(bk, tt)];
-      const uint32_t t = tt - sg.tile_prefix;
-      const uint32_t nv = chunk_valid(sg.n, sg.chunk, j);
-      const int64_t left = (int64_t)nv - (int64_t)t * kTile;
-      if (left <= 0) continue;
-      const int m = (int)(left < kTile ? left : kTile);
-      const size_t off = (size_t)j * sg.chunk + (size_t)t * kTile;
-      float x[kIter][4];
-      load_tile(sg.g + E * cm.emu_stride_g + off, m, x);
-      float* rp = sg.r ? sg.r + E * cm.emu_stride_r + off : nullptr;
-      if (rp) {
-        float rr[kIter][4];
-        load_tile(rp, m, rr);
-#pragma unroll
-        for (int jj = 0; jj < kIter; ++jj)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) x[jj][e] = rr[jj][e] + x[jj][e];
-      }
-      float meta[2];
-      uint32_t frag[kIter];
-      encode_tile<ALG, B>(x, m, fp.P, sg.id, off, fp.P.salt + (uint32_t)(R * 256), s, meta, frag);
-      if (rp) store_tile(rp, m, x);
-      stage_frags<B>(s.codes, frag);
-      __syncthreads();
-      store_payload_tile<ALG, B>(dslot + sg.pay_off, sg.chunk, t, m, nv, meta, fp.P.tau, s);
-      __syncthreads();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[j]) + (size_t)R * G + b, cm.epoch);
-    }
-  }
+  // phase 1: push
+  encode_phases<ALG, B, HP_TOPO_PS>(bk, cm, fp, sm, R, E, status);
 
   // phase 2: server for chunk R: sum the N payloads in rank order, re-encode, broadcast
   for (int q = 0; q < N; ++q)
     wait_flag(my_flags + (size_t)q * G + b, cm.epoch, cm.timeout_ns, status,
-              HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)q << 8) | (b & 255), ws);
-  for (uint32_t tt = b; tt < bk.tiles_total; tt += G) {
-    const SegDev& sg = bk.seg[find_seg(bk, tt)];
-    const uint32_t t = tt - sg.tile_prefix;
-    const uint32_t nv = chunk_valid(sg.n, sg.chunk, R);
-    const int64_t left = (int64_t)nv - (int64_t)t * kTile;
-    if (left <= 0) continue;
-    const int m = (int)(left < kTile ? left : kTile);
-    const size_t coff = (size_t)t * kTile;  // offset inside the owned chunk
-    float x[kIter][4];
-    for (int q = 0; q < N; ++q)
-      decode_into<ALG, B>(my_inbox + (size_t)q * bk.slot_bytes + sg.pay_off, sg.chunk, t, m,
-                          fp.P.tau, q > 0, x);
-    float* rp = sg.sr ? sg.sr + E * cm.emu_stride_sr + coff : nullptr;
-    if (rp) {
-      float rr[kIter][4];
-      load_tile(rp, m, rr);
+              HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)q << 8) | (b & 255), sm.ws);
+  {
+    Cursor cur;
+    cursor_begin(bk, G, b, 0, R, cur);
+    TileRef tr;
+    while (cursor_next(bk, G, b, cur, tr)) {
+      const SegDev& sg = bk.seg[tr.seg];
+      for (uint32_t u = 0; u < tr.cnt; ++u) {
+        const int m = tile_valid(tr, u);
+        const uint32_t t = tr.t0 + u;
+        const size_t coff = (size_t)t * kTile;  // offset inside the owned chunk
+        float x[kIter][4];
+        for (int q = 0; q < N; ++q)
+          decode_into<ALG, B>(my_inbox + (size_t)q * bk.slot_bytes + sg.pay_off, sg.chunk, t, m,
+                              fp.P.tau, q > 0, x);
+        float* rp = sg.sr ? sg.sr + E * cm.emu_stride_sr + coff : nullptr;
+        if (rp) {
+          float rr[kIter][4];
+          load_tile(rp, m, rr);
 #pragma unroll
-      for (int jj = 0; jj < kIter; ++jj)
+          for (int jj = 0; jj < kIter; ++jj)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) x[jj][e] = rr[jj][e] + x[jj][e];
+            for (int e = 0; e < 4; ++e) x[jj][e] = rr[jj][e] + x[jj][e];
+        }
+        float meta[2];
+        uint32_t frag[kIter];
+        encode_tile<ALG, B>(x, m, fp.P, sg.id, (size_t)R * sg.chunk + coff,
+                            fp.P.salt + (uint32_t)(R * 256 + 1), s, meta, frag);
+        if (rp) store_tile(rp, m, x);
+        stage_frags<B>(s.codes, frag);
+        __syncthreads();
+        for (int q = 0; q < N; ++q) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) +
+                         (size_t)(N + R) * bk.slot_bytes + sg.pay_off;
+          store_payload_tile<ALG, B>(dst, sg.chunk, t, m, tr.nv, meta, fp.P.tau, s);
+        }
+        __syncthreads();
+      }
     }
-    float meta[2];
-    uint32_t frag[kIter];
-    encode_tile<ALG, B>(x, m, fp.P, sg.id, (size_t)R * sg.chunk + coff,
-                        fp.P.salt + (uint32_t)(R * 256 + 1), s, meta, frag);
-    if (rp) store_tile(rp, m, x);
-    stage_frags<B>(s.codes, frag);
-    __syncthreads();
-    for (int q = 0; q < N; ++q) {
-      uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) +
-                     (size_t)(N + R) * bk.slot_bytes + sg.pay_off;
-      store_payload_tile<ALG, B>(dst, sg.chunk, t, m, nv, meta, fp.P.tau, s);
-    }
-    __syncthreads();
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -312,25 +522,7 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   // phase 3: pull: decode every owner's reduced chunk
   for (int i = 0; i < N; ++i) {
     const int j = (R + i) % N;
-    wait_flag(my_flags + (size_t)(N + j) * G + b, cm.epoch, cm.timeout_ns, status,
-              HP_STATUS_TIMEOUT | (2u << 16) | ((uint32_t)j << 8) | (b & 255), ws);
-    const uint8_t* slot = my_inbox + (size_t)(N + j) * bk.slot_bytes;
-    for (uint32_t tt = b; tt < bk.tiles_total; tt += G) {
-      const SegDev& sg = bk.seg[find_seg(bk, tt)];
-      const uint32_t t = tt - sg.tile_prefix;
-      const uint32_t nv = chunk_valid(sg.n, sg.chunk, j);
-      const int64_t left = (int64_t)nv - (int64_t)t * kTile;
-      if (left <= 0) continue;
-      const int m = (int)(left < kTile ? left : kTile);
-      const size_t off = (size_t)j * sg.chunk + (size_t)t * kTile;
-      float x[kIter][4];
-      decode_into<ALG, B>(slot + sg.pay_off, sg.chunk, t, m, fp.P.tau, false, x);
-#pragma unroll
-      for (int jj = 0; jj < kIter; ++jj)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) x[jj][e] = x[jj][e] * fp.inv_n;
-      store_tile(sg.out + E * cm.emu_stride_out + off, m, x);
-    }
+    decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N + j, j, status);
   }
 }
 
@@ -352,10 +544,10 @@ static int build_bucket(int alg, int bits, const HpSeg* segs, int nseg, int nran
     d.n = (uint32_t)n;
     d.chunk = (uint32_t)chunk;
     d.tiles = (uint32_t)(chunk / kTile);
-    d.tile_prefix = (uint32_t)tiles;
+    d.tile_prefix = (uint32_t)tiles;  // counted in super-tiles
     d.pay_off = (uint32_t)pay;
     d.id = segs[i].id;
-    tiles += d.tiles;
+    tiles += (d.tiles + kSuper - 1) / kSuper;
     pay += align_up(dense_payload_bytes(alg, bits, chunk), 128);
     if (pay > 0xFFFFFFFFull || tiles > 0x7FFFFFFFull) return HP_ERR_TOO_LARGE;
   }
@@ -374,20 +566,24 @@ static int launch_fused(int topo, const BucketDev& bk, const HpComm& cm, const F
                         int ctas, cudaStream_t st) {
   void (*kern)(const BucketDev, const HpComm, const FusedParams) =
       topo == HP_TOPO_RING ? ring_dense_kernel<ALG, B> : ps_dense_kernel<ALG, B>;
+  const size_t smem = sizeof(FusedSmem);
+  cudaError_t e0 = cudaFuncSetAttribute((const void*)kern,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e0 != cudaSuccess) return (int)e0;
   if (cm.emulate) {
     int dev = 0, sms = 0, per_sm = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, 0);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
     if (e != cudaSuccess) return (int)e;
     if ((long long)ctas * cm.nranks > (long long)per_sm * sms) return HP_ERR_RESIDENCY;
     void* args[] = {(void*)&bk, (void*)&cm, (void*)&fp};
     e = cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas, cm.nranks), dim3(kThreads),
-                                    args, 0, st);
+                                    args, smem, st);
     return (int)e;
   }
-  kern<<<dim3(ctas, 1), kThreads, 0, st>>>(bk, cm, fp);
+  kern<<<dim3(ctas, 1), kThreads, smem, st>>>(bk, cm, fp);
   return (int)cudaGetLastError();
 }
 

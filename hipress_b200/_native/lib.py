@@ -135,6 +135,9 @@ def cuda():
     _sig(L.hp_cuda_peer_store, C.c_int, vp, vp, C.c_uint64, C.c_int, vp)
     _sig(L.hp_cuda_wait_probe, C.c_int, vp, C.c_uint32, C.c_uint64, vp, vp)
     _sig(L.hp_cuda_set_flag, C.c_int, vp, C.c_uint32, vp)
+    _sig(L.hp_cuda_partition_stream_create, C.c_int, C.c_int, C.c_int, C.c_int,
+         C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.c_void_p))
+    _sig(L.hp_cuda_partition_stream_destroy, C.c_int, vp, vp)
     for name, sig in _CUDA_OPTIONAL.items():
         if hasattr(L, name):
             _sig(getattr(L, name), *sig)

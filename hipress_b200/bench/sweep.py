@@ -91,14 +91,40 @@ def sweep_fused(sizes, iters, ranks, ctas, out):
                 del b, G, Rr, O
 
 
+def run_single(alg, topo, mbytes, ctas, iters, out):
+    """One rank, one tensor, one fused launch per iteration (the case to hand to
+    a profiler): encode + local hand-off + decode of `mbytes` of fp32 gradient."""
+    peaks = measured_peaks()
+    flush = L2Flusher()
+    c = Compressor(alg)
+    ef = "residual" in c.spec.state_names()
+    n = mbytes * 1024 * 1024 // 4
+    b = FusedDenseBucket(c.spec, topo, [n], 1, 0, ctas=ctas).bind_local("cuda")
+    g = torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
+    r = torch.zeros(n, device="cuda") if ef else None
+    o = torch.empty(n, device="cuda")
+    t = time_cuda(lambda: b.launch([g], [r] if ef else None, [o]), iters=iters, flush=flush)
+    b.check_status()
+    nbytes = (8.0 + (8.0 if ef else 0.0)) * n
+    gbs = nbytes / (t["median_ms"] * 1e-3) / 1e9
+    row = {"kernel": f"{topo}_{alg}_1rank", "mbytes": mbytes, "ctas": b.ctas,
+           "ms": round(t["median_ms"], 5), "gbs": round(gbs, 1),
+           "frac_hbm": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}
+    out.append(row)
+    print(json.dumps(row), flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", choices=["ops", "fused", "all"], default="all")
+    ap.add_argument("--what", choices=["ops", "fused", "single", "all"], default="all")
+    ap.add_argument("--alg", default="tbq")
+    ap.add_argument("--topo", default="ring")
+    ap.add_argument("--mbytes", type=int, default=256)
     ap.add_argument("--min-kb", type=int, default=4)
     ap.add_argument("--max-mb", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--ranks", type=int, default=8)
-    ap.add_argument("--ctas", type=int, default=72, help="CTAs per emulated rank")
+    ap.add_argument("--ctas", type=int, default=32, help="CTAs per emulated rank")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
     sizes = []
@@ -107,6 +133,8 @@ def main(argv=None):
         sizes.append(s)
         s *= 4
     out = []
+    if a.what == "single":
+        run_single(a.alg, a.topo, a.mbytes, a.ctas, a.iters, out)
     if a.what in ("ops", "all"):
         sweep_ops(sizes, a.iters, out)
     if a.what in ("fused", "all"):

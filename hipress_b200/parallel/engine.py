@@ -79,6 +79,7 @@ class Bucket:
     impl: object = None
     flat: torch.Tensor | None = None
     work: object = None
+    stream: object = None
 
 
 def _flat(t: torch.Tensor) -> torch.Tensor:
@@ -248,9 +249,16 @@ class GradSyncEngine:
         if use_fused_kernels and not self.comp.spec.sparse:
             from .fused import FusedDenseBucket
             from .symm import SymmetricArena
-            impls = [FusedDenseBucket(self.comp.spec, cfg.topology, [s.n for s in b.segs], self.N,
-                                      self.R, ctas=cfg.ctas, timeout_s=cfg.timeout_s)
-                     for b in fused_buckets]
+            self._make_partition_stream()
+            impls = []
+            for i, b in enumerate(fused_buckets):
+                # buckets that complete while backward still runs go to the SM
+                # partition; the last one has nothing left to overlap with
+                on_part = cfg.partition_sms > 0 and i < len(fused_buckets) - 1
+                b.stream = self.part_stream if on_part else self.comm_stream
+                impls.append(FusedDenseBucket(
+                    self.comp.spec, cfg.topology, [s.n for s in b.segs], self.N, self.R,
+                    ctas=cfg.partition_ctas if on_part else cfg.ctas, timeout_s=cfg.timeout_s))
             total = sum(i.region_bytes() for i in impls) + 4096
             self.arena = SymmetricArena(total, self.group)
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -265,6 +273,25 @@ class GradSyncEngine:
             if not b.fused and self.N > 1:
                 b.flat = torch.zeros(sum(e.numel for e in b.entries), dtype=torch.float32,
                                      device=self.device)
+
+    def _make_partition_stream(self):
+        """Stream bound to a green context of cfg.partition_sms SMs; falls back to
+        the ordinary communication stream when the driver refuses."""
+        self.part_stream, self._green = self.comm_stream, None
+        if self.cfg.partition_sms <= 0:
+            return
+        import ctypes as C
+        from .._native import lib as _lib
+        st, sms, g = C.c_void_p(), C.c_int(), C.c_void_p()
+        rc = _lib.cuda().hp_cuda_partition_stream_create(
+            self.device.index if self.device.index is not None else torch.cuda.current_device(),
+            self.cfg.partition_sms, -1, C.byref(st), C.byref(sms), C.byref(g))
+        if rc != 0 or not st.value:
+            log.warning("SM partition unavailable; fused kernels share the whole GPU")
+            return
+        self._green = (st.value, g.value)
+        self.partition_sms = sms.value
+        self.part_stream = torch.cuda.ExternalStream(st.value, device=self.device)
 
     def _setup_fused_sparse(self, fused_buckets) -> bool:
         try:
@@ -308,10 +335,11 @@ class GradSyncEngine:
     def _launch(self, b: Bucket):
         b.launched = True
         if self.on_cuda:
+            st = b.stream or self.comm_stream
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream())
-            self.comm_stream.wait_event(ev)
-            ctx = torch.cuda.stream(self.comm_stream)
+            st.wait_event(ev)
+            ctx = torch.cuda.stream(st)
         else:
             import contextlib
             ctx = contextlib.nullcontext()
@@ -337,7 +365,7 @@ class GradSyncEngine:
                 sr_ptrs.append(None if sr is None else sr.data_ptr())
                 ids.append(s.seg_id)
             b.impl.launch_ptrs(g_ptrs, r_ptrs, g_ptrs, sr_ptrs, step=self.step_no, tensor_ids=ids,
-                               stream=self.comm_stream)
+                               stream=b.stream or self.comm_stream)
             self.launch_count += 1
         else:
             views = []
@@ -374,6 +402,9 @@ class GradSyncEngine:
             self._launch(b)
         self._next = len(self.buckets)
         if self.on_cuda:
+            part = getattr(self, "part_stream", None)
+            if part is not None and part is not self.comm_stream:
+                self.comm_stream.wait_stream(part)
             with torch.cuda.stream(self.comm_stream):
                 for b in self.buckets:
                     if not b.fused:
@@ -461,3 +492,9 @@ class GradSyncEngine:
         if self.arena is not None:
             self.arena.close()
             self.arena = None
+        if getattr(self, "_green", None):
+            from .._native import lib as _lib
+            torch.cuda.synchronize()
+            self.part_stream = self.comm_stream
+            _lib.cuda().hp_cuda_partition_stream_destroy(*self._green)
+            self._green = None

@@ -68,6 +68,15 @@ def test_ps_emulated(name, kw, N):
     _run("ps", name, kw, N, [70001, 4096, 300, 1 << 17])
 
 
+@pytest.mark.parametrize("topology", ["ring", "ps"])
+@pytest.mark.parametrize("N", [1, 2, 8])
+@pytest.mark.parametrize("name,kw", ALGS[:3])
+def test_emulated_aligned_tensors_use_bulk_prefetch(name, kw, N, topology):
+    """Every tile is full and 16-byte aligned, so all loads go through the
+    shared-memory prefetch pipeline (several tiles per CTA, across phases)."""
+    _run(topology, name, kw, N, [1 << 19, 65536 + 4096 * 3, 8192 * N], steps=3, ctas=4)
+
+
 def test_mean_of_many_steps_tracks_uncompressed_average():
     """Error feedback: over many steps the compressed ring delivers the same total."""
     torch.manual_seed(0)
