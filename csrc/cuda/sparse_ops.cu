@@ -25,6 +25,7 @@
 
 #include "hipress/capi.h"
 #include "hipress/common.h"
+#include "hipress/noalloc.h"
 
 namespace hipress {
 
@@ -350,6 +351,36 @@ int hp_cuda_sparse_encode(int alg, const float* g, float* a, float* u, uint64_t 
                           int max_ctas, void* stream) {
   return sparse_encode_impl(alg, g, a, u, n, k, kmax, momentum, update, out,
                             static_cast<uint32_t*>(workspace), max_ctas, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant (see hipress/noalloc.h): the scratch lives in this
+// file-scope device array.  In host code the name below is only a handle for
+// the runtime, never a device address; the address each GPU gave the array is
+// fetched once per device with cudaGetSymbolAddress and passed to the kernels.
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kWsWords];
+
+static uint32_t* g_noalloc_ptr[64];  // per device, filled on the first call there
+
+uint64_t hp_cuda_noalloc_scratch_bytes(void) { return (uint64_t)kWsWords * 4; }
+
+int hp_cuda_sparse_encode_noalloc(int alg, const float* g, float* a, float* u, uint64_t n,
+                                  uint64_t k, uint64_t kmax, float momentum, int update,
+                                  uint8_t* out, int max_ctas, void* stream) {
+  if (n > HP_NOALLOC_MAX_ELEMS) return HP_ERR_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return HP_ERR_BAD_ARG;
+  if (!g_noalloc_ptr[dev]) {  // set-up: once per device, with that device current
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!p) return HP_ERR_BAD_ARG;
+    g_noalloc_ptr[dev] = static_cast<uint32_t*>(p);
+  }
+  return sparse_encode_impl(alg, g, a, u, n, k, kmax, momentum, update, out, g_noalloc_ptr[dev],
+                            max_ctas, (cudaStream_t)stream);
 }
 
 // accumulate=0: out is zero-filled first.  accumulate=1: out[idx] += val*scale.

@@ -51,7 +51,8 @@ int hp_cuda_device_count() {
 
 const char* hp_cuda_error_string(int code) {
   if (code == HP_ERR_BAD_ARG) return "hipress: bad argument";
-  if (code == HP_ERR_TOO_LARGE) return "hipress: bucket too large";
+  if (code == HP_ERR_TOO_LARGE)
+    return "hipress: input larger than this entry point supports (bucket or element limit)";
   if (code == HP_ERR_RESIDENCY) return "hipress: emulated ranks would not be co-resident";
   return cudaGetErrorString((cudaError_t)code);
 }
