@@ -1,0 +1,181 @@
+"""CompLL: DSL front end, CUDA emitter, and (on a GPU) the generated kernels
+against plain PyTorch restatements of the DSL semantics."""
+import importlib.util
+import os
+import shutil
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from hipress_b200.compll import CompileError, generate, generate_files, parse, tokenize
+from hipress_b200.compll import frontend as F
+
+PSE = Path(__file__).resolve().parents[1] / "hipress_b200" / "compll" / "pse"
+REF_PSE = Path(__file__).resolve().parents[1] / "baseline" / "_ref" / "src" / "CompLL" / "GCGen" / "pse"
+HAVE_NVCC = shutil.which("nvcc") is not None or os.path.exists("/usr/local/cuda/bin/nvcc")
+
+
+def test_lexer_float_literals_and_operators():
+    toks = [(t.kind, t.text) for t in tokenize("x = 0.01 + 3e-2 << 2; // c\n y>=1")]
+    assert ("float", "0.01") in toks and ("float", "3e-2") in toks
+    assert ("op", "<<") in toks and ("op", ">=") in toks
+    assert all(t[1] != "c" for t in toks)  # comment stripped
+
+
+def test_parser_builds_typed_tree():
+    fn = parse((PSE / "TernGradEncode.pse").read_text())
+    assert fn.name == "TernGradEncode"
+    assert [(t.name, t.vector, n) for t, n in fn.params] == [
+        ("float", True, "gradient"), ("uint8", True, "compressed"), ("uint8", False, "bitwidth")]
+    kinds = [type(s).__name__ for s in fn.body]
+    assert kinds.count("Decl") >= 7 and kinds[-1] == "Assign"
+    q = [s for s in fn.body if isinstance(s, F.Decl) and s.name == "Q"][0]
+    assert q.type.vector and isinstance(q.type.bits, F.Name) and isinstance(q.init, F.Map)
+
+
+def test_literal_bitwidth_and_precedence():
+    fn = parse("void f(float* g, uint8* c){ uint<2>* Q = map(range(g.size), h); int a = 1 + 2 * 3 << 1; }")
+    q = fn.body[0]
+    assert isinstance(q.type.bits, F.Num) and q.type.bits.text == "2"
+    a = fn.body[1].init
+    assert isinstance(a, F.Binary) and a.op == "<<" and a.a.op == "+" and a.a.b.op == "*"
+
+
+@pytest.mark.parametrize("src,msg", [
+    ("void f(float* g){ foo x = 1; }", "unrecognized|expected|typename"),
+    ("void f(float* g){ float a = reduce(g, 0); }", "three arguments"),
+    ("void f(float* g, uint8* c){ uint<2>* Q = map(range(g.size), nolambda); c = concat(Q); }", "lambda"),
+    ("void f(float* g){ float a = $; }", "unexpected character"),
+])
+def test_errors_carry_a_message(src, msg):
+    import re
+    with pytest.raises(CompileError) as e:
+        generate(src).body_source()
+    assert re.search(msg, str(e.value))
+
+
+def test_unsupported_framework_is_an_error_not_ignored():
+    em = generate((PSE / "TernGradDecode.pse").read_text())
+    with pytest.raises(CompileError):
+        em.register_source("mxnet")
+    assert "def TernGradDecode(" in em.register_source("torch")
+
+
+def test_emitter_structure():
+    em = generate((PSE / "OnebitEncode.pse").read_text())
+    # source order is kept: map, reduce, map, map
+    assert [s[0] for s in em.stages] == ["map", "reduce", "map", "map"]
+    body = em.body_source()
+    assert "compll_rand01" not in body and "__shfl_xor_sync" in body
+    em2 = generate((PSE / "TernGradEncode.pse").read_text())
+    # two reduces fused into one pass; header offsets 0,1,2,6 then codes at 10
+    assert [s[0] for s in em2.stages] == ["reduce", "map"] and len(em2.stages[0][1]) == 2
+    assert em2.concats[0][1] == [("bitwidth", 0), ("pad", 1), ("lo", 2), ("hi", 6)]
+    assert em2.syms["Q"].alias == ("compressed", 10)
+    assert "compll_rand01" in em2.body_source()
+
+
+@pytest.mark.skipif(not REF_PSE.exists(), reason="reference tree not present")
+def test_reference_sources_are_accepted_unchanged(tmp_path):
+    for name in ("TernGradEncode", "TernGradDecode"):
+        em = generate((REF_PSE / f"{name}.pse").read_text())
+        assert em.fn.name == name
+        assert "__global__" in em.body_source()
+    enc = generate((REF_PSE / "TernGradEncode.pse").read_text())
+    # the 10-byte header of the reference: bitwidth, tail, min, max at 0,1,2,6
+    assert enc.concats[0][1] == [("bitwidth", 0), ("tail", 1), ("min", 2), ("max", 6)]
+
+
+@pytest.mark.skipif(not HAVE_NVCC, reason="nvcc not available")
+def test_generated_code_compiles_for_sm100a(tmp_path):
+    for f in sorted(PSE.glob("*.pse")):
+        files = generate_files(f, tmp_path, build=True)
+        assert files[-1].name.startswith("lib") and files[-1].exists()
+
+
+# ------------------------------------------------------------------ GPU
+def _load(tmp_path, name, src_dir=PSE):
+    generate_files(src_dir / f"{name}.pse", tmp_path, build=True)
+    spec = importlib.util.spec_from_file_location(name, tmp_path / name / f"{name}.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return getattr(mod, name)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+@pytest.mark.parametrize("n", [7, 4096, 100003])
+def test_generated_terngrad_roundtrip(tmp_path, bits, n):
+    enc, dec = _load(tmp_path, "TernGradEncode"), _load(tmp_path, "TernGradDecode")
+    torch.manual_seed(n)
+    g = torch.randn(n, device="cuda")
+    per = 8 // bits
+    comp = torch.zeros(10 + (n + per - 1) // per, dtype=torch.uint8, device="cuda")
+    enc(g, comp, bits, seed=3)
+    out = torch.full((n,), 7.0, device="cuda")
+    dec(comp, out)
+    torch.cuda.synchronize()
+    hdr = comp[:10].cpu()
+    assert hdr[0].item() == bits and hdr[1].item() == (per - n % per) % per
+    lo, hi = hdr[2:6].view(torch.float32).item(), hdr[6:10].view(torch.float32).item()
+    assert lo == g.min().item() and hi == g.max().item()
+    gap = (hi - lo) / (2 ** bits - 1)
+    assert (out - g).abs().max().item() <= gap * (1 + 1e-5) + 1e-6
+    # decoded values sit on the quantisation grid
+    lv = (out - lo) / gap
+    assert (lv - lv.round()).abs().max().item() < 1e-3
+    # same seed, same payload; the stochastic rounding is unbiased on average
+    comp2 = torch.zeros_like(comp)
+    enc(g, comp2, bits, seed=3)
+    assert torch.equal(comp, comp2)
+    if bits == 2 and n > 50000:
+        assert abs((out - g).mean().item()) < 0.02 * gap
+
+
+@pytest.mark.gpu
+def test_generated_onebit_and_tbq_with_error_feedback(tmp_path):
+    n = 50001
+    torch.manual_seed(0)
+    g = torch.randn(n, device="cuda") * 0.02
+    r0 = torch.randn(n, device="cuda") * 0.005
+    x = g + r0
+    # onebit
+    enc, dec = _load(tmp_path, "OnebitEncode"), _load(tmp_path, "OnebitDecode")
+    r = r0.clone()
+    comp = torch.zeros(4 + (n + 7) // 8, dtype=torch.uint8, device="cuda")
+    enc(g, r, comp)
+    out = torch.empty(n, device="cuda")
+    dec(comp, out)
+    scale = comp[:4].cpu().view(torch.float32).item()
+    assert scale == pytest.approx(x.abs().mean().item(), rel=1e-4)
+    assert torch.equal(out < 0, x < 0)
+    assert torch.allclose(out + r, x, atol=1e-6)
+    # tbq
+    enc, dec = _load(tmp_path, "TbqEncode"), _load(tmp_path, "TbqDecode")
+    r = r0.clone()
+    comp = torch.zeros(4 + (n + 3) // 4, dtype=torch.uint8, device="cuda")
+    enc(g, r, comp, 0.01)
+    dec(comp, out)
+    want = torch.where(x >= 0.01, 0.01, torch.where(x <= -0.01, -0.01, 0.0))
+    assert torch.allclose(out, want.float())
+    assert torch.allclose(out + r, x, atol=1e-7)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not REF_PSE.exists(), reason="reference tree not present")
+def test_reference_dsl_sources_run(tmp_path):
+    """The reference's own TernGrad sources, generated and run unchanged (n is a
+    multiple of 4 and bitwidth 2, the case its tail arithmetic covers)."""
+    enc = _load(tmp_path, "TernGradEncode", REF_PSE)
+    dec = _load(tmp_path, "TernGradDecode", REF_PSE)
+    n = 4096 * 3
+    g = torch.randn(n, device="cuda")
+    comp = torch.zeros(10 + n // 4, dtype=torch.uint8, device="cuda")
+    enc(g, comp, 2)
+    out = torch.empty(n, device="cuda")
+    dec(comp, out)
+    gap = (g.max() - g.min()).item() / 3
+    inside = g < g.max() - gap  # the source does not clamp a round-up at the maximum
+    assert (out - g)[inside].abs().max().item() <= gap * 1.001
