@@ -3,7 +3,8 @@ from .bert import BertConfig, BertForMaskedLM, bert_large, bert_tiny  # noqa: F4
 from .resnet import ResNet50, resnet50  # noqa: F401
 from .vgg import VGG19, vgg19  # noqa: F401
 
-MODELS = {"vgg19": vgg19, "resnet50": resnet50, "bert_large": bert_large, "bert-large": bert_large}
+MODELS = {"vgg19": vgg19, "resnet50": resnet50, "bert_large": bert_large, "bert-large": bert_large,
+          "bert_tiny": bert_tiny}
 
 
 def get_model(name: str, **kw):

@@ -35,6 +35,7 @@ from ..secopa.planner import read_plan
 from . import comm
 from .host_schedule import HostSchedule, SegView
 from .simulate import chunk_elems
+from ..utils.timeline import Timeline, nvtx_range
 
 log = logging.getLogger("hipress")
 MAX_SEGS = 40
@@ -144,6 +145,7 @@ class GradSyncEngine:
         self._begin()
         self.launch_count = 0
         self.bytes_sent = 0
+        self.timeline = Timeline()
 
     # ------------------------------------------------------------------ plan
     def _make_entries(self, named):
@@ -343,11 +345,16 @@ class GradSyncEngine:
         else:
             import contextlib
             ctx = contextlib.nullcontext()
-        with ctx:
+        with ctx, nvtx_range(f"hipress.bucket{b.index}.{'fused' if b.fused else 'plain'}"):
+            tok = self.timeline.begin(f"bucket{b.index}", torch.cuda.current_stream()) \
+                if self.timeline.enabled else None
             if b.fused:
                 self._launch_fused(b)
             else:
                 self._launch_plain(b)
+            if tok is not None:
+                self.timeline.end(tok, torch.cuda.current_stream(), step=self.step_no,
+                                  fused=b.fused, elems=sum(e.numel for e in b.entries))
 
     def _launch_fused(self, b: Bucket):
         grads = {id(e): self._grad(e) for e in b.entries}
@@ -486,6 +493,7 @@ class GradSyncEngine:
                 "kernel_launches": self.launch_count}
 
     def close(self):
+        self.timeline.dump(self.R)
         for h in self._hooks:
             h.remove()
         self._hooks = []

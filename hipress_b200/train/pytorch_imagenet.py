@@ -1,0 +1,77 @@
+"""PyTorch training script with synthetic data, flags as in the reference's
+``horovod-torch/imageNet/pytorch_imagenet.py`` (``--batch-size --epochs
+--num-iterations --model --algorithm``, README.md:184-186 of mark14wu/hipress).
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m hipress_b200.train.pytorch_imagenet --model vgg19 --algorithm tbq --batch-size 32
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+
+import torch
+
+import hipress_b200 as hp
+from hipress_b200.config import add_hipress_args, config_from_args
+from hipress_b200.train.harness import build_job
+from hipress_b200.utils import MetricsWriter, engine_metrics, load_checkpoint, save_checkpoint, setup_logging
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="hipress_b200 synthetic-data training")
+    ap.add_argument("--model", default="vgg19")
+    ap.add_argument("--batch-size", type=int, default=None, help="per-GPU batch")
+    ap.add_argument("--epochs", type=int, default=1)
+    ap.add_argument("--num-iterations", type=int, default=20, help="iterations per epoch")
+    ap.add_argument("--seq-len", type=int, default=128)
+    ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--fp32", action="store_true", help="no bf16 autocast")
+    ap.add_argument("--checkpoint-dir", default=None)
+    ap.add_argument("--resume", action="store_true")
+    ap.add_argument("--metrics", default=None, help="JSONL file for per-step metrics")
+    add_hipress_args(ap)
+    a = ap.parse_args(argv)
+    hp.init()
+    log = setup_logging()
+    cfg = config_from_args(a)
+    job = build_job(a.model, cfg, batch=a.batch_size, seq_len=a.seq_len, lr=a.lr,
+                    dtype=torch.float32 if a.fp32 else torch.bfloat16)
+    start_epoch = 0
+    if a.resume and a.checkpoint_dir:
+        info = load_checkpoint(a.checkpoint_dir, job.model, job.optimizer, map_location=job.device)
+        start_epoch = info["epoch"]
+        log.info("resumed from %s at epoch %d", a.checkpoint_dir, start_epoch)
+    mw = MetricsWriter(a.metrics)
+    log.info("model %s, %d GPUs, batch %d/GPU, %s", a.model, hp.size(), job.batch,
+             engine_metrics(job.optimizer.engine))
+    cuda = job.device.type == "cuda"
+    hosts = [job.host_batch(100 * hp.rank() + i) for i in range(4)]
+    step = 0
+    for epoch in range(start_epoch, a.epochs):
+        if cuda:
+            torch.cuda.synchronize()
+        t0 = time.time()
+        for it in range(a.num_iterations):
+            x, y = job.to_device(*hosts[it % 4])
+            loss = job.step(x, y)
+            step += 1
+            if it % 10 == 9 or it == a.num_iterations - 1:
+                lv = loss.item()
+                dt = time.time() - t0
+                ips = job.batch * hp.size() * (it + 1) / dt
+                log.info("epoch %d iter %d loss %.4f  %.1f samples/s", epoch, it + 1, lv, ips)
+                mw.step(step, epoch=epoch, loss=lv, samples_per_s=round(ips, 1),
+                        **engine_metrics(job.optimizer.engine))
+        if a.checkpoint_dir:
+            save_checkpoint(a.checkpoint_dir, job.model, job.optimizer, epoch=epoch + 1, step=step)
+    job.optimizer.engine.check() if cuda else None
+    mw.close()
+    job.optimizer.close()
+    hp.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

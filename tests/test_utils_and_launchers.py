@@ -1,0 +1,158 @@
+"""Checkpoint round trip, metrics, host-side failure detection (gloo ranks, no GPU),
+launcher command construction, SeCoPa plan consumption by the engine."""
+import json
+import os
+import time
+
+import pytest
+import torch
+
+from _mp import spawn
+
+SHAPES = [(64, 100), (64,), (5000,)]
+
+
+def _ckpt_worker(rank, world, d):
+    import hipress_b200 as hp
+    from hipress_b200.utils import load_checkpoint, save_checkpoint
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(100, 64), torch.nn.Linear(64, 80))
+    opt = hp.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9),
+                                  model.named_parameters(), algorithm="tbq", comp_threshold=1000,
+                                  threshold=0.001)
+    g = torch.Generator().manual_seed(rank)
+    for _ in range(3):
+        model(torch.randn(8, 100, generator=g)).pow(2).mean().backward()
+        opt.step()
+        opt.zero_grad()
+    save_checkpoint(d, model, opt, epoch=2, step=3)
+    before = opt.engine.state_dict()
+    w_before = model[0].weight.detach().clone()
+    # a fresh job resumes
+    model2 = torch.nn.Sequential(torch.nn.Linear(100, 64), torch.nn.Linear(64, 80))
+    opt2 = hp.DistributedOptimizer(torch.optim.SGD(model2.parameters(), lr=0.1, momentum=0.9),
+                                   model2.named_parameters(), algorithm="tbq", comp_threshold=1000,
+                                   threshold=0.001)
+    info = load_checkpoint(d, model2, opt2)
+    after = opt2.engine.state_dict()
+    same = all(torch.equal(before["tensors"][k]["residual"], after["tensors"][k]["residual"])
+               for k in before["tensors"])
+    nz = any(float(v["residual"].abs().sum()) > 0 for v in before["tensors"].values())
+    return {"info": info, "same": same, "nonzero": nz,
+            "weights": torch.equal(w_before, model2[0].weight.detach()),
+            "momentum": len(opt2.optimizer.state_dict()["state"]) > 0,
+            "step": opt2.engine.step_no}
+
+
+def test_checkpoint_roundtrip_with_compressor_state(tmp_path):
+    res = spawn(_ckpt_worker, 2, str(tmp_path))
+    for r in res:
+        assert r["info"]["epoch"] == 2 and r["info"]["step"] == 3
+        assert r["same"] and r["nonzero"] and r["weights"] and r["momentum"] and r["step"] == 3
+    assert sorted(os.listdir(tmp_path)) == ["model.pt", "rank0.pt", "rank1.pt"]
+
+
+def _health_worker(rank, world, mode):
+    from hipress_b200.utils.health import HealthMonitor, PeerFailure, default_store
+    import torch.distributed as dist
+    mon = HealthMonitor(default_store(), rank, world, interval_s=0.05, timeout_s=0.6)
+    dist.barrier()
+    time.sleep(0.3)
+    mon.check()  # everybody alive
+    dist.barrier()
+    out = "ok"
+    if rank == world - 1:
+        if mode == "leave":
+            mon.leave()          # orderly exit between steps
+        else:
+            mon.pause()          # host thread stops beating (a hung rank)
+        time.sleep(2.0)
+    else:
+        t0 = time.time()
+        while time.time() - t0 < 3.0:
+            try:
+                mon.check()
+            except PeerFailure as e:
+                out = (e.ranks, "left" if "left" in str(e) else "silent", round(time.time() - t0, 1))
+                break
+            time.sleep(0.05)
+    mon.close()
+    return out
+
+
+@pytest.mark.parametrize("mode", ["leave", "silent"])
+def test_peer_failure_is_detected_on_the_host(mode):
+    res = spawn(_health_worker, 3, mode)
+    for r in res[:2]:
+        assert r != "ok", "failure was not detected"
+        ranks, kind, dt = r
+        assert ranks == [2] and kind == ("left" if mode == "leave" else "silent") and dt < 2.5
+
+
+def test_launcher_builds_a_local_torchrun_command(capsys):
+    from hipress_b200.train import data_parallel_train as L
+    rc = L.main(["--numprocess", "4", "--servers", "localhost:4", "--model", "vgg19", "--topo", "Ring",
+                 "--comp-alg", "tbq", "--comp-threshold", "262144", "--horovodrun", "--interface",
+                 "eth0", "--dry-run"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "--nproc-per-node=4" in out and "--comp-alg tbq" in out and "--topo Ring" in out
+    with pytest.raises(SystemExit):
+        L.main(["--numprocess", "2", "--servers", "node1:1,node2:1", "--dry-run"])
+
+
+def test_engine_consumes_a_secopa_plan(tmp_path):
+    import hipress_b200 as hp
+    params = [("a", torch.nn.Parameter(torch.zeros(30000))), ("b", torch.nn.Parameter(torch.zeros(30000))),
+              ("c", torch.nn.Parameter(torch.zeros(10)))]
+    plan = tmp_path / "plan.txt"
+    plan.write_text("a,30000,y,3\nb,30000,n,4\nc,10,n,4\n")
+    opt = hp.DistributedOptimizer(torch.optim.SGD([p for _, p in params], lr=1.0), params,
+                                  algorithm="tbq", plan=str(plan), comp_threshold=1)
+    eng = opt.engine
+    by = {e.name: e for e in eng.entries}
+    assert by["a"].compress and not by["b"].compress and not by["c"].compress
+    fused = [b for b in eng.buckets if b.fused]
+    assert len(fused) == 1 and [(s.lo, s.hi) for s in fused[0].segs] == [(0, 12288), (12288, 24576), (24576, 30000)]
+    for _, p in params:
+        p.grad = torch.full_like(p, 0.5)
+    opt.step()
+    assert torch.allclose(params[0][1].detach(), torch.full((30000,), -0.01))  # one tbq level
+    assert torch.allclose(params[1][1].detach(), torch.full((30000,), -0.5))
+    bad = tmp_path / "bad.txt"
+    bad.write_text("a,7,y,1\n")
+    with pytest.raises(ValueError):
+        hp.DistributedOptimizer(torch.optim.SGD([p for _, p in params], lr=1.0), params,
+                                algorithm="tbq", plan=str(bad))
+
+
+def test_metrics_writer_and_engine_metrics(tmp_path):
+    import hipress_b200 as hp
+    from hipress_b200.utils import MetricsWriter, engine_metrics
+    p = torch.nn.Parameter(torch.zeros(8192))
+    opt = hp.DistributedOptimizer(torch.optim.SGD([p], lr=1.0), [("w", p)], algorithm="onebit",
+                                  comp_threshold=1)
+    p.grad = torch.randn(8192)
+    opt.step()
+    m = engine_metrics(opt.engine)
+    assert m["compression_ratio"] > 25 and m["residual_norm"] > 0
+    mw = MetricsWriter(str(tmp_path / "m.jsonl"))
+    mw.step(1, loss=1.5, **m)
+    mw.close()
+    rec = json.loads((tmp_path / "m.jsonl").read_text().splitlines()[0])
+    assert rec["step"] == 1 and rec["loss"] == 1.5 and rec["backend"] == "host"
+
+
+def test_training_script_runs_end_to_end_on_cpu(tmp_path):
+    from hipress_b200.train import pytorch_imagenet as T
+    import hipress_b200 as hp
+    rc = T.main(["--model", "bert_tiny", "--batch-size", "2", "--seq-len", "16", "--num-iterations", "3",
+                 "--fp32", "--algorithm", "onebit", "--comp-threshold", "1000",
+                 "--checkpoint-dir", str(tmp_path / "ck"), "--metrics", str(tmp_path / "m.jsonl")])
+    assert rc == 0
+    assert (tmp_path / "ck" / "model.pt").exists() and (tmp_path / "ck" / "rank0.pt").exists()
+    rec = json.loads((tmp_path / "m.jsonl").read_text().splitlines()[-1])
+    assert rec["loss"] == rec["loss"] and rec["compression_ratio"] > 1
+    rc = T.main(["--model", "bert_tiny", "--batch-size", "2", "--seq-len", "16", "--num-iterations", "1",
+                 "--epochs", "2", "--fp32", "--algorithm", "onebit", "--comp-threshold", "1000",
+                 "--checkpoint-dir", str(tmp_path / "ck"), "--resume"])
+    assert rc == 0
