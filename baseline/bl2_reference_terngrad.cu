@@ -1,0 +1,86 @@
+// Baseline BL2: the reference's own generated TernGrad encode / decode pair
+// (thrust), compiled unmodified for sm_100a and timed per size on the stream.
+// The two headers are included from a copy of the reference tree given with
+// -I <ref>/src/CompLL/GCGen/output/TernGradEncode (and .../TernGradDecode); this
+// file adds only the timing harness.  The reference code is numerically wrong
+// (integer min/max reduction, wrong element index, bit-order mismatch), so only
+// its time is a baseline, not its output.
+//
+//   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 \
+//        -I baseline/_ref/src/CompLL/GCGen/output/TernGradEncode \
+//        -I baseline/_ref/src/CompLL/GCGen/output/TernGradDecode \
+//        baseline/bl2_reference_terngrad.cu -o baseline/bl2_reference_terngrad
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include <cuda_runtime.h>
+#include <thrust/execution_policy.h>
+
+#include "TernGradEncode_body.h"
+#include "TernGradDecode_body.h"
+
+int main(int argc, char** argv) {
+  const size_t max_bytes = argc > 1 ? strtoull(argv[1], nullptr, 10) << 20 : (size_t)256 << 20;
+  const int iters = 5;
+  cudaStream_t st;
+  cudaStreamCreate(&st);
+  float* flush;
+  const size_t flush_n = (size_t)64 << 20;
+  cudaMalloc(&flush, flush_n * 4);
+  printf("[");
+  bool first = true;
+  for (size_t bytes = 4096; bytes <= max_bytes; bytes *= 4) {
+    const int n = (int)(bytes / 4);
+    std::vector<float> h(n);
+    unsigned s = 12345u;
+    for (int i = 0; i < n; ++i) {
+      s = s * 1664525u + 1013904223u;
+      h[i] = ((s >> 8) / 16777216.0f - 0.5f) * 4.0f;
+    }
+    float* g;
+    uint8_t* c;
+    const int csize = 10 + (n + 3) / 4 + 4;
+    cudaMalloc(&g, bytes);
+    cudaMalloc(&c, csize);
+    cudaMemcpy(g, h.data(), bytes, cudaMemcpyHostToDevice);
+    auto pol = thrust::cuda::par.on(st);
+    float enc_ms[iters], dec_ms[iters];
+    cudaEvent_t a, b;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    for (int it = -2; it < iters; ++it) {
+      cudaMemsetAsync(flush, it & 1, flush_n * 4, st);
+      cudaStreamSynchronize(st);
+      cudaEventRecord(a, st);
+      TernGradEncode_body(g, n, c, csize, (uint8_t)2, pol, (void*)st);
+      cudaEventRecord(b, st);
+      cudaStreamSynchronize(st);
+      float ms;
+      cudaEventElapsedTime(&ms, a, b);
+      if (it >= 0) enc_ms[it] = ms;
+      cudaMemsetAsync(flush, it & 1, flush_n * 4, st);
+      cudaStreamSynchronize(st);
+      cudaEventRecord(a, st);
+      TernGradDecode_body(c, csize, g, n, pol, (void*)st);
+      cudaEventRecord(b, st);
+      cudaStreamSynchronize(st);
+      cudaEventElapsedTime(&ms, a, b);
+      if (it >= 0) dec_ms[it] = ms;
+    }
+    auto med = [&](float* v) {
+      for (int i = 0; i < iters; ++i)
+        for (int j = i + 1; j < iters; ++j)
+          if (v[j] < v[i]) { float t = v[i]; v[i] = v[j]; v[j] = t; }
+      return v[iters / 2];
+    };
+    printf("%s\n {\"bytes\": %zu, \"ref_encode_ms\": %.5f, \"ref_decode_ms\": %.5f}", first ? "" : ",",
+           bytes, med(enc_ms), med(dec_ms));
+    first = false;
+    cudaFree(g);
+    cudaFree(c);
+    if (cudaGetLastError() != cudaSuccess) break;
+  }
+  printf("\n]\n");
+  return 0;
+}

@@ -145,3 +145,28 @@ def _run_mismatch(rank, world):
 def test_parameter_order_mismatch_is_detected():
     res = _spawn(_run_mismatch, 2)
     assert all("disagree" in r for r in res)
+
+
+def _run_ddp_hook(rank, world):
+    import hipress_b200 as hp
+    from hipress_b200.parallel.hooks import FlatSyncer, ddp_comm_hook
+    from torch.nn.parallel import DistributedDataParallel as DDP
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.ReLU(), torch.nn.Linear(256, 10))
+    ddp = DDP(model)
+    syncer = FlatSyncer(hp.HipressConfig(algorithm="tbq", topology="ring", comp_threshold=1024,
+                                         threshold=0.001))
+    ddp.register_comm_hook(syncer, ddp_comm_hook)
+    g = torch.Generator().manual_seed(rank)
+    for _ in range(2):
+        ddp(torch.randn(16, 64, generator=g)).pow(2).mean().backward()
+    grads = [p.grad.clone() for p in model.parameters()]
+    res = sum(float(s[0]["residual"].abs().sum()) for s in syncer.state.values())
+    return {"grads": grads, "resid": res}
+
+
+def test_ddp_comm_hook_keeps_replicas_identical():
+    res = _spawn(_run_ddp_hook, 2)
+    for a, b in zip(res[0]["grads"], res[1]["grads"]):
+        assert torch.equal(a, b)
+    assert res[0]["resid"] > 0  # error feedback is active
