@@ -40,9 +40,12 @@ int main(int argc, char** argv) {
     }
     float* g;
     uint8_t* c;
-    const int csize = 10 + (n + 3) / 4 + 4;
-    cudaMalloc(&g, bytes);
-    cudaMalloc(&c, csize);
+    // exact size: the reference decoder derives the element count from the buffer
+    // size ((8*bytes - 80)/bitwidth - tail), so any slack makes it write past the
+    // gradient; both buffers are over-allocated by a page for the same reason
+    const int csize = 10 + n / 4;
+    cudaMalloc(&g, bytes + 4096);
+    cudaMalloc(&c, csize + 4096);
     cudaMemcpy(g, h.data(), bytes, cudaMemcpyHostToDevice);
     auto pol = thrust::cuda::par.on(st);
     float enc_ms[iters], dec_ms[iters];

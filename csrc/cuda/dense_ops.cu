@@ -71,28 +71,50 @@ dense_encode_kernel(const float* __restrict__ g, float* __restrict__ r,
   }
 }
 
+// Decode is write bound (4 B/element out, bits in).  Each CTA iteration handles
+// kDecBatch tiles and issues all their payload loads before the first store, so
+// one L2 round trip is exposed per batch instead of per tile.
+constexpr int kDecBatch = 4;
+
 template <int ALG, int B>
 __global__ void __launch_bounds__(kThreads)
 dense_decode_kernel(const uint8_t* __restrict__ payload, float* __restrict__ out, uint32_t n,
                     float tau, float scale, int accumulate) {
   const uint32_t tiles = (uint32_t)num_tiles(n);
   PayloadView pv = payload_view(const_cast<uint8_t*>(payload), ALG, n);
-  for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x) {
-    const uint32_t start = t * kTile;
-    const int m = (int)min((uint32_t)kTile, n - start);
-    float meta[2];
-    load_meta<ALG>(pv.meta, t, meta);
-    const uint8_t* tc = pv.codes + (size_t)t * (kTile * B / 8);
-    float x[kIter][4];
-    if (accumulate) load_tile(out + start, m, x);
+  for (uint32_t t0 = blockIdx.x * kDecBatch; t0 < tiles; t0 += gridDim.x * kDecBatch) {
+    uint32_t fr[kDecBatch][kIter];
+    float mt[kDecBatch][2];
 #pragma unroll
-    for (int j = 0; j < kIter; ++j) {
-      float d[4];
-      decode_frag<ALG, B>(load_frag<B>(tc, j, m), meta, tau, d);
+    for (int u = 0; u < kDecBatch; ++u) {
+      const uint32_t t = t0 + u;
+      if (t < tiles) {
+        const int m = (int)min((uint32_t)kTile, n - t * kTile);
+        load_meta<ALG>(pv.meta, t, mt[u]);
+        const uint8_t* tc = pv.codes + (size_t)t * (kTile * B / 8);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) x[j][e] = accumulate ? x[j][e] + d[e] * scale : d[e] * scale;
+        for (int j = 0; j < kIter; ++j) fr[u][j] = load_frag<B>(tc, j, m);
+      }
     }
-    store_tile(out + start, m, x);
+#pragma unroll
+    for (int u = 0; u < kDecBatch; ++u) {
+      const uint32_t t = t0 + u;
+      if (t < tiles) {
+        const uint32_t start = t * kTile;
+        const int m = (int)min((uint32_t)kTile, n - start);
+        float x[kIter][4];
+        if (accumulate) load_tile(out + start, m, x);
+#pragma unroll
+        for (int j = 0; j < kIter; ++j) {
+          float d[4];
+          decode_frag<ALG, B>(fr[u][j], mt[u], tau, d);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            x[j][e] = accumulate ? x[j][e] + d[e] * scale : d[e] * scale;
+        }
+        store_tile(out + start, m, x);
+      }
+    }
   }
 }
 
@@ -111,7 +133,7 @@ static int launch_encode(const float* g, float* r, const uint8_t* in, uint8_t* o
 template <int ALG, int B>
 static int launch_decode(const uint8_t* p, float* out, uint64_t n, float tau, float scale,
                          int acc, int max_ctas, cudaStream_t st) {
-  const uint64_t tiles = num_tiles(n);
+  const uint64_t tiles = (num_tiles(n) + kDecBatch - 1) / kDecBatch;
   int grid = (int)(tiles < (uint64_t)max_ctas ? tiles : (uint64_t)max_ctas);
   if (grid < 1) grid = 1;
   dense_decode_kernel<ALG, B><<<grid, kThreads, 0, st>>>(p, out, (uint32_t)n, tau, scale, acc);

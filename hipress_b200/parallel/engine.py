@@ -358,7 +358,23 @@ class GradSyncEngine:
 
     def _launch_fused(self, b: Bucket):
         grads = {id(e): self._grad(e) for e in b.entries}
-        if b.impl is not None:
+        if b.impl is not None and self.comp.spec.sparse:
+            g_ptrs, a_ptrs, u_ptrs, sr_ptrs = [], [], [], []
+            for s in b.segs:
+                e = s.entry
+                g_ptrs.append(grads[id(e)].data_ptr() + 4 * s.lo)
+                acc = e.state["accum_v"] if "accum_v" in e.state else e.state["residual"]
+                a_ptrs.append(acc.data_ptr() + 4 * s.lo)
+                u = e.state.get("momentum_u")
+                u_ptrs.append(None if u is None else u.data_ptr() + 4 * s.lo)
+                sst = e.server_state[s.part]
+                if sst.get("_scratch"):
+                    sst["residual"].zero_()
+                sr_ptrs.append(sst["residual"].data_ptr())
+            b.impl.launch_ptrs(g_ptrs, a_ptrs, u_ptrs, g_ptrs, sr_ptrs,
+                               stream=b.stream or self.comm_stream)
+            self.launch_count += 10
+        elif b.impl is not None:
             g_ptrs, r_ptrs, sr_ptrs, ids = [], [], [], []
             rname = "residual"
             for s in b.segs:
@@ -460,7 +476,8 @@ class GradSyncEngine:
             d = {k: v.detach().cpu().clone() for k, v in e.state.items()}
             for i, sst in enumerate(e.server_state):
                 for k, v in sst.items():
-                    d[f"server_{k}.{i}"] = v.detach().cpu().clone()
+                    if torch.is_tensor(v) and not sst.get("_scratch"):
+                        d[f"server_{k}.{i}"] = v.detach().cpu().clone()
             d["step"] = self.step_no
             out[e.name] = d
         return {"world_size": self.N, "rank": self.R, "algorithm": self.cfg.algorithm,
@@ -481,6 +498,8 @@ class GradSyncEngine:
                     v.copy_(d[k])
             for i, sst in enumerate(e.server_state):
                 for k, v in sst.items():
+                    if not torch.is_tensor(v):
+                        continue
                     key = f"server_{k}.{i}"
                     if key in d and d[key].numel() == v.numel():
                         v.copy_(d[key])

@@ -1,0 +1,76 @@
+"""Fused sparse parameter-server kernels (DGC / GradDrop) with the N ranks played
+phase by phase on one GPU, against the lock-step simulation on the CPU oracle."""
+import pytest
+import torch
+
+from hipress_b200.ops import Compressor
+from hipress_b200.parallel.fused_sparse import FusedSparseBucket
+from hipress_b200.parallel.simulate import chunk_elems, simulate_ps
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("N", [1, 2, 4, 8])
+@pytest.mark.parametrize("name", ["dgc", "graddrop"])
+def test_sparse_ps_emulated(name, N):
+    torch.manual_seed(99 + N)
+    sizes = [200003, 8192, 300, 1 << 18]
+    c = Compressor(name, ratio=0.01)
+    b = FusedSparseBucket(c.spec, sizes, N, 0, ctas=8, emulate=True).bind_local("cuda")
+    total = sum(sizes)
+    chunks = [chunk_elems(s, N) for s in sizes]
+    offs = [sum(sizes[:i]) for i in range(len(sizes))]
+    coffs = [sum(chunks[:i]) for i in range(len(sizes))]
+    G = torch.zeros(N, total, device="cuda")
+    A = torch.zeros(N, total, device="cuda")
+    U = torch.zeros(N, total, device="cuda") if name == "dgc" else None
+    O = torch.zeros(N, total, device="cuda")
+    SR = torch.zeros(N, sum(chunks), device="cuda")
+    cpu_states = [[c.new_state(s, "cpu") for s in sizes] for _ in range(N)]
+    cpu_server = [[{"residual": torch.zeros(ch)} for ch in chunks] for _ in range(N)]
+    for step in range(3):
+        Gc = torch.randn(N, total)
+        G.copy_(Gc)
+        b.launch_ptrs([G[0, o:].data_ptr() for o in offs], [A[0, o:].data_ptr() for o in offs],
+                      [U[0, o:].data_ptr() for o in offs] if U is not None else None,
+                      [O[0, o:].data_ptr() for o in offs], [SR[0, o:].data_ptr() for o in coffs],
+                      strides=(total, total, total, sum(chunks)))
+        torch.cuda.synchronize()
+        b.check_status()
+        for i, (o, s) in enumerate(zip(offs, sizes)):
+            gl = [Gc[r, o:o + s].contiguous() for r in range(N)]
+            ref = simulate_ps(c, gl, [cpu_states[r][i] for r in range(N)],
+                              [cpu_server[r][i] for r in range(N)])
+            for r in range(N):
+                got = O[r, o:o + s].cpu()
+                assert torch.allclose(got, ref[r], rtol=1e-5, atol=1e-7), (name, N, step, i, r,
+                                                                          (got - ref[r]).abs().max())
+                assert torch.equal(O[r, o:o + s], O[0, o:o + s])
+                acc_name = "accum_v" if name == "dgc" else "residual"
+                assert torch.allclose(A[r, o:o + s].cpu(), cpu_states[r][i][acc_name], rtol=1e-5,
+                                      atol=1e-7)
+            ch = chunks[i]
+            for r in range(N):
+                assert torch.allclose(SR[r, coffs[i]:coffs[i] + ch].cpu(), cpu_server[r][i]["residual"],
+                                      rtol=1e-5, atol=1e-7)
+        assert (O[0] != 0).sum().item() > 0
+
+
+def test_sparse_ps_through_the_optimizer_single_rank():
+    import hipress_b200 as hp
+    torch.manual_seed(3)
+    p = torch.nn.Parameter(torch.zeros(100000, device="cuda"))
+    opt = hp.DistributedOptimizer(torch.optim.SGD([p], lr=1.0), [("w", p)], algorithm="dgc",
+                                  topology="ps", comp_threshold=1024, ratio=0.01)
+    assert opt.engine.backend == "fused" and opt.engine.buckets[0].impl is not None
+    g = torch.randn(100000, device="cuda")
+    p.grad = g.clone()
+    opt.step()
+    torch.cuda.synchronize()
+    opt.engine.check()
+    sent = (p.detach() != 0)
+    assert sent.sum().item() == 1000
+    top = torch.topk(g.abs(), 1000).indices
+    assert sent[top].all()
+    assert torch.allclose(-p.detach()[top], g[top])
+    opt.close()
