@@ -102,7 +102,7 @@ __device__ __forceinline__ uint32_t chunk_valid(uint32_t n, uint32_t chunk, int 
 }
 
 // ------------------------------------------------------------ shared memory
-constexpr int kStages = 3;  // tiles of g (+ r) in flight per CTA
+constexpr int kStages = 2;  // tiles of g (+ r) in flight per CTA
 
 struct FusedSmem {
   alignas(128) float g[kStages][kTile];
@@ -431,7 +431,7 @@ __device__ __forceinline__ void fused_prologue(FusedSmem& sm) {
 
 // ------------------------------------------------------------------------ ring
 template <int ALG, int B>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 ring_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
@@ -450,7 +450,7 @@ ring_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
 
 // -------------------------------------------------------------------------- PS
 template <int ALG, int B>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
