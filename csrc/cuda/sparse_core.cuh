@@ -143,14 +143,22 @@ __device__ __forceinline__ void pass_body(const float* __restrict__ a, uint64_t 
   const uint32_t prefix = PASS == 1 ? bin0 : ((bin0 << 11) | bin1);
   const int shift = PASS == 1 ? 19 : 8;
   const bool vec = (reinterpret_cast<uintptr_t>(a) & 15) == 0;
-  const uint64_t stride = (uint64_t)nctas * kSpThreads * 4;
-  for (uint64_t i = ((uint64_t)cta * kSpThreads + threadIdx.x) * 4; i < n; i += stride) {
-    const float4 av = ld4(a, i, n, vec);
-    const float e[4] = {av.x, av.y, av.z, av.w};
+  // 4096-element tiles, four independent 16-byte loads per thread in flight
+  const uint64_t tiles = (n + 4095) / 4096;
+  for (uint64_t t = cta; t < tiles; t += nctas) {
+    float4 av[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint32_t key = abs_key(e[q]);
-      if (i + q < n && (key >> shift) == prefix) atomicAdd(&sh[digit_of(key, PASS)], 1u);
+    for (int j = 0; j < 4; ++j)
+      av[j] = ld4(a, t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4, n, vec);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint64_t i = t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4;
+      const float e[4] = {av[j].x, av[j].y, av[j].z, av[j].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t key = abs_key(e[q]);
+        if (i + q < n && (key >> shift) == prefix) atomicAdd(&sh[digit_of(key, PASS)], 1u);
+      }
     }
   }
   __syncthreads();
