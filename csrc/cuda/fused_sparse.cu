@@ -34,6 +34,9 @@ struct SpSeg {
   float* out;  // averaged gradient (may alias g)
   float* sr;   // server accumulator for the owned chunk [chunk]
   uint32_t n, chunk, kmax, pay_off;
+  uint32_t cap;         // candidate pairs per (tensor, chunk) unit
+  uint64_t cand_push;   // first push unit's candidate list, in pairs from the region start
+  uint64_t cand_srv;    // the server unit's candidate list
 };
 
 struct SpBucket {
@@ -42,6 +45,7 @@ struct SpBucket {
   int alg;
   float ratio, momentum, inv_n;
   uint64_t slot_bytes;
+  uint64_t cand_pairs;  // candidate pairs of all units of one rank
 };
 
 __device__ __forceinline__ uint32_t sp_chunk_valid(uint32_t n, uint32_t chunk, int c) {
@@ -59,9 +63,13 @@ __device__ __forceinline__ void write_empty_header(uint8_t* out, int alg) {
 
 // ---------------------------------------------------------------- push
 // unit y = seg * N + owner
-template <int STAGE>  // 0: update + hist0, 1: hist1, 2: hist2, 3: emit + flag
+// STAGE 0: update + hist0   1: split (certain elements go to the owner at once)
+//       2,3: digit passes on the candidate list   4: candidate compaction + flag
+//       5,6,7: full-array passes and compaction, only after a candidate overflow
+template <int STAGE>
 __global__ void __launch_bounds__(kSpThreads)
-sp_push_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_all) {
+sp_push_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_all,
+               uint8_t* cand_all) {
   __shared__ uint32_t sh[kBins];
   __shared__ FindSmem fs;
   __shared__ EmitSmem es;
@@ -70,45 +78,64 @@ sp_push_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_al
   const SpSeg& sg = bk.seg[si];
   const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, c);
   uint32_t* ws = ws_all + (size_t)blockIdx.y * kWsWords;
+  float* cand_val = reinterpret_cast<float*>(cand_all + (sg.cand_push + (uint64_t)c * sg.cap) * 8);
+  uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + sg.cap);
   const size_t off = (size_t)c * sg.chunk;
   const float* g = sg.g + E * cm.emu_stride_g + off;
   float* a = sg.a + E * cm.emu_stride_r + off;
   float* u = sg.u ? sg.u + E * cm.emu_stride_r + off : nullptr;
   const uint32_t k = (uint32_t)sparse_k(len, bk.ratio);
+  uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[c]) + (size_t)R * bk.slot_bytes + sg.pay_off;
+  EmitDst d;
+  d.n = 1;
+  d.out[0] = dst;
+  bool last = false;
   if (STAGE == 0) {
     if (len == 0) return;
     if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
     else pass0_body<1>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
+    return;
   } else if (STAGE == 1) {
     if (len == 0) return;
-    pass_body<1>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
-  } else if (STAGE == 2) {
-    if (len == 0) return;
-    pass_body<2>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
-  } else {
-    uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[c]) + (size_t)R * bk.slot_bytes + sg.pay_off;
-    bool last;
+    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, es, blockIdx.x, gridDim.x);
+    return;
+  } else if (STAGE == 2 || STAGE == 3) {
+    if (len == 0 || ws[kWsOverflow]) return;
+    if (STAGE == 2) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    return;
+  } else if (STAGE == 4) {
     if (len == 0) {
       last = blockIdx.x == 0 && threadIdx.x == 0;
       if (last) write_empty_header(dst, bk.alg);
     } else {
-      EmitDst d;
-      d.n = 1;
-      d.out[0] = dst;
-      last = emit_body(bk.alg, a, u, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+      if (ws[kWsOverflow]) return;
+      last = emit_body(bk.alg, cand_val, u, ws[kWsCandCount], k, sg.kmax, d, ws, fs, es, blockIdx.x,
+                       gridDim.x, cand_idx, a, len);
     }
-    if (last) {  // thread 0 of the CTA that completed the unit
-      __threadfence_system();
-      st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[c]) + (size_t)R * bk.nseg + si, cm.epoch);
-    }
+  } else if (STAGE == 5 || STAGE == 6) {
+    if (len == 0 || !ws[kWsOverflow]) return;
+    if (STAGE == 5) pass_body<1>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    else pass_body<2>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    return;
+  } else {
+    if (len == 0 || !ws[kWsOverflow]) return;
+    last = emit_body(bk.alg, a, u, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+  }
+  if (last) {  // thread 0 of the CTA that completed the unit
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[c]) + (size_t)R * bk.nseg + si, cm.epoch);
   }
 }
 
 // -------------------------------------------------------------- server
 // unit y = seg; the owned chunk is chunk R
-template <int STAGE>  // 0: wait + scatter-add, 1..3: hist passes, 4: emit to all + flags
+// STAGE 0: wait + scatter-add   1: hist0   2: split (to every rank)   3,4: candidate
+//       digit passes   5: candidate compaction + flags   6,7,8: overflow path
+template <int STAGE>
 __global__ void __launch_bounds__(kSpThreads)
-sp_server_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_all) {
+sp_server_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_all,
+                 uint8_t* cand_all) {
   __shared__ uint32_t sh[kBins];
   __shared__ FindSmem fs;
   __shared__ EmitSmem es;
@@ -118,9 +145,17 @@ sp_server_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_
   const SpSeg& sg = bk.seg[si];
   const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, R);
   uint32_t* ws = ws_all + (size_t)blockIdx.y * kWsWords;
+  float* cand_val = reinterpret_cast<float*>(cand_all + sg.cand_srv * 8);
+  uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + sg.cap);
   float* acc = sg.sr + E * cm.emu_stride_sr;
   uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   const uint32_t k = (uint32_t)sparse_k(len, bk.ratio);
+  EmitDst d;
+  d.n = N;
+  for (int q = 0; q < N; ++q)
+    d.out[q] = reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) + (size_t)(N + R) * bk.slot_bytes +
+               sg.pay_off;
+  bool last = false;
   if (STAGE == 0) {
     wait_init(wst);
     const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(cm.flags[R]);
@@ -132,36 +167,46 @@ sp_server_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_
     for (int q = 0; q < N; ++q)
       scatter_body(inbox + (size_t)q * bk.slot_bytes + sg.pay_off, acc, len, sg.kmax, 1.0f, 2,
                    blockIdx.x, gridDim.x);
+    return;
   } else if (STAGE == 1) {
     if (len == 0) return;
     pass0_body<0>(nullptr, acc, nullptr, len, 0.0f, ws, sh, blockIdx.x, gridDim.x);
+    return;
   } else if (STAGE == 2) {
     if (len == 0) return;
-    pass_body<1>(acc, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
-  } else if (STAGE == 3) {
-    if (len == 0) return;
-    pass_body<2>(acc, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
-  } else {
-    EmitDst d;
-    d.n = N;
-    for (int q = 0; q < N; ++q)
-      d.out[q] = reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) + (size_t)(N + R) * bk.slot_bytes +
-                 sg.pay_off;
-    bool last;
+    split_body(acc, nullptr, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, es, blockIdx.x,
+               gridDim.x);
+    return;
+  } else if (STAGE == 3 || STAGE == 4) {
+    if (len == 0 || ws[kWsOverflow]) return;
+    if (STAGE == 3) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    return;
+  } else if (STAGE == 5) {
     if (len == 0) {
       last = blockIdx.x == 0 && threadIdx.x == 0;
       if (last)
         for (int q = 0; q < N; ++q) write_empty_header(d.out[q], bk.alg);
     } else {
-      last = emit_body(bk.alg, acc, nullptr, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+      if (ws[kWsOverflow]) return;
+      last = emit_body(bk.alg, cand_val, nullptr, ws[kWsCandCount], k, sg.kmax, d, ws, fs, es,
+                       blockIdx.x, gridDim.x, cand_idx, acc, len);
     }
-    if (last) {
-      __threadfence_system();
-      for (int q = 0; q < N; ++q)
-        st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + q) % N]) +
-                           (size_t)(N + R) * bk.nseg + si,
-                       cm.epoch);
-    }
+  } else if (STAGE == 6 || STAGE == 7) {
+    if (len == 0 || !ws[kWsOverflow]) return;
+    if (STAGE == 6) pass_body<1>(acc, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    else pass_body<2>(acc, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    return;
+  } else {
+    if (len == 0 || !ws[kWsOverflow]) return;
+    last = emit_body(bk.alg, acc, nullptr, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+  }
+  if (last) {
+    __threadfence_system();
+    for (int q = 0; q < N; ++q)
+      st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + q) % N]) +
+                         (size_t)(N + R) * bk.nseg + si,
+                     cm.epoch);
   }
 }
 
@@ -200,7 +245,7 @@ static int build_sp_bucket(int alg, float ratio, float momentum, const HpSeg* se
                            void* const* accs, void* const* us, int nseg, int nranks, SpBucket& bk) {
   if (nseg < 1 || nseg > HP_MAX_SEGS || nranks < 1 || nranks > HP_MAX_RANKS) return HP_ERR_BAD_ARG;
   if (alg != kDgc && alg != kGradDrop) return HP_ERR_BAD_ARG;
-  uint64_t pay = 0;
+  uint64_t pay = 0, cand = 0;
   for (int i = 0; i < nseg; ++i) {
     const uint64_t n = segs[i].n;
     if (n == 0 || n > 0xFFFFF000ull) return HP_ERR_BAD_ARG;
@@ -215,6 +260,11 @@ static int build_sp_bucket(int alg, float ratio, float momentum, const HpSeg* se
     d.chunk = (uint32_t)chunk;
     d.kmax = (uint32_t)sparse_k(chunk, ratio);
     d.pay_off = (uint32_t)pay;
+    d.cap = (uint32_t)align_up(8ull * d.kmax + 4096, 32);
+    d.cand_push = cand;
+    cand += (uint64_t)d.cap * nranks;
+    d.cand_srv = cand;
+    cand += d.cap;
     pay += align_up(sparse_payload_bytes(d.kmax), 128);
     if (pay > 0xFFFFFFFFull) return HP_ERR_TOO_LARGE;
   }
@@ -224,6 +274,7 @@ static int build_sp_bucket(int alg, float ratio, float momentum, const HpSeg* se
   bk.momentum = momentum;
   bk.inv_n = 1.0f / (float)nranks;
   bk.slot_bytes = pay;
+  bk.cand_pairs = cand;
   return 0;
 }
 
@@ -245,7 +296,8 @@ int hp_fused_sparse_layout(float ratio, const uint64_t* ns, int nseg, int nranks
   if (inbox_bytes) *inbox_bytes = bk.slot_bytes * 2ull * nranks;
   if (flag_words) *flag_words = 2ull * nranks * nseg;
   // push units (nseg * nranks) + server units (nseg), per emulated rank
-  if (ws_bytes) *ws_bytes = (uint64_t)(nseg * nranks + nseg) * kWsWords * 4;
+  if (ws_bytes)
+    *ws_bytes = align_up((uint64_t)(nseg * nranks + nseg) * kWsWords * 4, 256) + bk.cand_pairs * 8;
   return 0;
 }
 
@@ -256,41 +308,65 @@ int hp_fused_sparse_layout(float ratio, const uint64_t* ns, int nseg, int nranks
 int hp_cuda_fused_sparse_ps(int alg, float ratio, float momentum, const HpSeg* segs,
                             void* const* us, int nseg, const HpComm* comm, void* ws, int ctas,
                             void* stream) {
-  if (!comm || ctas < 1 || ctas > 1024) return HP_ERR_BAD_ARG;
+  if (!comm || ctas > 1024) return HP_ERR_BAD_ARG;
   SpBucket bk;
   const int N = comm->nranks;
   int rc = build_sp_bucket(alg, ratio, momentum, segs, nullptr, us, nseg, N, bk);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   const int ranks_here = comm->emulate ? N : 1;
-  const size_t ws_rank_words = (size_t)(nseg * N + nseg) * kWsWords;
-  cudaError_t e = cudaMemsetAsync(ws, 0, ws_rank_words * 4 * ranks_here, st);
-  if (e != cudaSuccess) return (int)e;
-  uint32_t* wsw = static_cast<uint32_t*>(ws);
-  const dim3 gpush(ctas, nseg * N), gsrv(ctas, nseg);
+  const size_t hist_words = (size_t)(nseg * N + nseg) * kWsWords;
+  const size_t hist_bytes = align_up(hist_words * 4, 256);
+  const size_t ws_rank_bytes = hist_bytes + bk.cand_pairs * 8;
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  for (int r = 0; r < ranks_here; ++r) {  // only the histogram blocks need clearing
+    cudaError_t e = cudaMemsetAsync(wsb + (size_t)r * ws_rank_bytes, 0, hist_words * 4, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  // ctas <= 0: size the grids so that every launch fills the GPU about four
+  // CTAs per SM, whatever the number of (tensor, owner) units
+  auto per_unit = [&](int units) {
+    if (ctas > 0) return ctas;
+    int c = (148 * 4 + units - 1) / units;
+    return c < 4 ? 4 : (c > 592 ? 592 : c);
+  };
+  const dim3 gpush(per_unit(nseg * N), nseg * N), gsrv(per_unit(nseg), nseg);
+  const dim3 cpush(gpush.x < 32 ? gpush.x : 32, nseg * N), csrv(gsrv.x < 32 ? gsrv.x : 32, nseg);
+  const dim3 gpull(per_unit(nseg * N) < 16 ? per_unit(nseg * N) : 16, nseg * N);
   // With emulated ranks every phase is issued for all ranks before the next one,
   // so a wait never targets a launch that is still queued behind it.
   for (int r = 0; r < ranks_here; ++r) {
     const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
-    uint32_t* w = wsw + (size_t)r * ws_rank_words;
-    sp_push_kernel<0><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
-    sp_push_kernel<1><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
-    sp_push_kernel<2><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
-    sp_push_kernel<3><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
+    uint32_t* w = reinterpret_cast<uint32_t*>(wsb + (size_t)r * ws_rank_bytes);
+    uint8_t* cd = wsb + (size_t)r * ws_rank_bytes + hist_bytes;
+    sp_push_kernel<0><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_push_kernel<1><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_push_kernel<2><<<cpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_push_kernel<3><<<cpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_push_kernel<4><<<cpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_push_kernel<5><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_push_kernel<6><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_push_kernel<7><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
   }
   for (int r = 0; r < ranks_here; ++r) {
     const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
-    uint32_t* w = wsw + (size_t)r * ws_rank_words + (size_t)nseg * N * kWsWords;
-    sp_server_kernel<0><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
-    sp_server_kernel<1><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
-    sp_server_kernel<2><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
-    sp_server_kernel<3><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
-    sp_server_kernel<4><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w);
+    uint32_t* w = reinterpret_cast<uint32_t*>(wsb + (size_t)r * ws_rank_bytes) +
+                  (size_t)nseg * N * kWsWords;
+    uint8_t* cd = wsb + (size_t)r * ws_rank_bytes + hist_bytes;
+    sp_server_kernel<0><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<1><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<2><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<3><<<csrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<4><<<csrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<5><<<csrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<6><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<7><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
+    sp_server_kernel<8><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
   }
   for (int r = 0; r < ranks_here; ++r) {
     const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
     sp_pull_kernel<0><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E);
-    sp_pull_kernel<1><<<dim3(4, nseg * N), kSpThreads, 0, st>>>(bk, *comm, R, E);
+    sp_pull_kernel<1><<<gpull, kSpThreads, 0, st>>>(bk, *comm, R, E);
   }
   return (int)cudaGetLastError();
 }

@@ -18,6 +18,8 @@ constexpr int kBins = 4096;
 constexpr int kWsOutCount = 3 * kBins + 0;
 constexpr int kWsTieCount = 3 * kBins + 1;
 constexpr int kWsDone = 3 * kBins + 2;
+constexpr int kWsCandCount = 3 * kBins + 3;  // candidates appended by the split pass
+constexpr int kWsOverflow = 3 * kBins + 4;   // candidate list did not fit: use the full passes
 constexpr int kWsWords = 3 * kBins + 16;
 
 __device__ __forceinline__ uint32_t digit_of(uint32_t key, int pass) {
@@ -181,10 +183,16 @@ struct EmitDst {
 
 // Compaction.  Tile = 4096 elements per CTA iteration, 16 per thread.  Returns
 // true in thread 0 of the CTA that finished last, after it wrote the headers.
+// With `remap` the scanned array `a` is a compacted candidate list: element i stands
+// for element remap[i] of the accumulator a_orig (and of u), which is what gets
+// reported and zeroed.
 __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float* __restrict__ u,
                                           uint64_t n, uint32_t k, uint32_t kmax, const EmitDst& dst,
                                           uint32_t* __restrict__ ws, FindSmem& fs, EmitSmem& es,
-                                          uint32_t cta, uint32_t nctas) {
+                                          uint32_t cta, uint32_t nctas,
+                                          const uint32_t* __restrict__ remap = nullptr,
+                                          float* __restrict__ a_orig = nullptr,
+                                          uint32_t n_orig = 0) {
   uint32_t bin0, k1, bin1, k2, bin2, need_eq;
   find_bin(ws, k, fs, bin0, k1);
   find_bin(ws + kBins, k1, fs, bin1, k2);
@@ -262,12 +270,15 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
           ++rank_eq;
         }
         if (pos < kmax) {
+          uint32_t where = remap ? remap[i + q] : (uint32_t)(i + q);
+          if (remap && where >= n_orig) where = 0;  // never index outside the accumulator
           for (int d = 0; d < dst.n; ++d) {
-            reinterpret_cast<uint32_t*>(dst.out[d] + 16)[pos] = (uint32_t)(i + q);
+            reinterpret_cast<uint32_t*>(dst.out[d] + 16)[pos] = where;
             reinterpret_cast<float*>(dst.out[d] + val_off)[pos] = e[4 * j + q];
           }
-          a[i + q] = 0.0f;
-          if (u) u[i + q] = 0.0f;
+          if (remap) a_orig[where] = 0.0f;
+          else a[i + q] = 0.0f;
+          if (u) u[where] = 0.0f;
         }
       }
     }
@@ -282,7 +293,7 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
       __threadfence();
       const uint32_t sent = atomicAdd(ws + kWsOutCount, 0u);
       WireHeader h;
-      h.n = (uint32_t)n;
+      h.n = remap ? n_orig : (uint32_t)n;  // always the length of the accumulator
       h.alg = (uint8_t)alg;
       h.bitwidth = 0;
       h.flags = 0;
@@ -294,6 +305,99 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
     }
   }
   return false;
+}
+
+// Split pass (after pass 0): everything above the threshold's 12-bit bin is
+// certainly among the k largest and is sent and zeroed at once; the elements of
+// that bin go to a compact candidate list (value + original index) on which the
+// remaining two digit passes and the final compaction run.  One pass over the
+// array instead of three.  A candidate list that does not fit raises the
+// overflow word and the full-array passes take over.
+__device__ __forceinline__ void split_body(float* __restrict__ a, float* __restrict__ u, uint64_t n,
+                                           uint32_t k, uint32_t kmax, const EmitDst& dst,
+                                           uint32_t* __restrict__ ws, float* __restrict__ cand_val,
+                                           uint32_t* __restrict__ cand_idx, uint32_t cand_cap,
+                                           FindSmem& fs, EmitSmem& es, uint32_t cta, uint32_t nctas) {
+  uint32_t bin0, k1;
+  find_bin(ws, k, fs, bin0, k1);
+  const size_t val_off = 16 + align_up(4ull * kmax, 16);
+  const bool vec = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(u)) & 15) == 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint64_t tiles = (n + 4095) / 4096;
+  for (uint64_t t = cta; t < tiles; t += nctas) {
+    float e[16];
+    uint32_t flag = 0;  // 2 bits per element: bit0 above the bin, bit1 inside it
+    uint32_t cnt = 0;   // low 16: above, high 16: inside
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint64_t i = t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4;
+      const float4 av = ld4(a, i, n, vec);
+      e[4 * j] = av.x; e[4 * j + 1] = av.y; e[4 * j + 2] = av.z; e[4 * j + 3] = av.w;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t bin = abs_key(e[4 * j + q]) >> 19;
+        if (i + q < n) {
+          if (bin > bin0) { flag |= 1u << (2 * (4 * j + q)); cnt += 1u; }
+          else if (bin == bin0) { flag |= 2u << (2 * (4 * j + q)); cnt += 1u << 16; }
+        }
+      }
+    }
+    uint32_t inc = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += y;
+    }
+    if (lane == 31) es.warp_tot[warp] = inc;
+    __syncthreads();
+    uint32_t wbase = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < kSpThreads / 32; ++w) {
+      const uint32_t wt = es.warp_tot[w];
+      if (w < warp) wbase += wt;
+      tot += wt;
+    }
+    const uint32_t excl = wbase + inc - cnt;
+    if (tot == 0) {
+      __syncthreads();
+      continue;
+    }
+    const uint32_t tot_gt = tot & 0xFFFFu, tot_in = tot >> 16;
+    if (threadIdx.x == 0) {
+      es.base_gt = tot_gt ? atomicAdd(ws + kWsOutCount, tot_gt) : 0u;
+      es.base_eq = tot_in ? atomicAdd(ws + kWsCandCount, tot_in) : 0u;
+      if (tot_in && es.base_eq + tot_in > cand_cap) ws[kWsOverflow] = 1u;
+    }
+    __syncthreads();
+    uint32_t pg = es.base_gt + (excl & 0xFFFFu);
+    uint32_t pc = es.base_eq + (excl >> 16);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint64_t i = t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t f = (flag >> (2 * (4 * j + q))) & 3u;
+        if (f & 1u) {
+          const uint32_t pos = pg++;
+          if (pos < kmax) {
+            for (int d = 0; d < dst.n; ++d) {
+              reinterpret_cast<uint32_t*>(dst.out[d] + 16)[pos] = (uint32_t)(i + q);
+              reinterpret_cast<float*>(dst.out[d] + val_off)[pos] = e[4 * j + q];
+            }
+            a[i + q] = 0.0f;
+            if (u) u[i + q] = 0.0f;
+          }
+        } else if (f & 2u) {
+          const uint32_t pos = pc++;
+          if (pos < cand_cap) {
+            cand_val[pos] = e[4 * j + q];
+            cand_idx[pos] = (uint32_t)(i + q);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
 }
 
 // out[idx] (+)= val * scale ; indices come from another rank: bounds-checked

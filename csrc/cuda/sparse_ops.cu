@@ -53,6 +53,66 @@ sparse_emit_kernel(int alg, float* __restrict__ a, float* __restrict__ u, uint64
   emit_body(alg, a, u, n, k, kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
 }
 
+// ---- candidate path: split pass, then digit passes and compaction on the list
+__global__ void __launch_bounds__(kSpThreads)
+sparse_split_kernel(float* __restrict__ a, float* __restrict__ u, uint64_t n, uint32_t k,
+                    uint32_t kmax, uint8_t* __restrict__ out, uint32_t* __restrict__ ws,
+                    float* __restrict__ cand_val, uint32_t* __restrict__ cand_idx, uint32_t cap) {
+  __shared__ FindSmem fs;
+  __shared__ EmitSmem es;
+  EmitDst d;
+  d.n = 1;
+  d.out[0] = out;
+  split_body(a, u, n, k, kmax, d, ws, cand_val, cand_idx, cap, fs, es, blockIdx.x, gridDim.x);
+}
+
+template <int PASS>
+__global__ void __launch_bounds__(kSpThreads)
+sparse_cand_pass_kernel(const float* __restrict__ cand_val, uint32_t k, uint32_t* __restrict__ ws) {
+  __shared__ uint32_t sh[kBins];
+  __shared__ FindSmem fs;
+  if (ws[kWsOverflow]) return;
+  pass_body<PASS>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+}
+
+__global__ void __launch_bounds__(kSpThreads)
+sparse_cand_emit_kernel(int alg, float* __restrict__ cand_val, const uint32_t* __restrict__ cand_idx,
+                        float* __restrict__ a, float* __restrict__ u, uint32_t k, uint32_t kmax,
+                        uint8_t* __restrict__ out, uint32_t* __restrict__ ws, uint64_t n) {
+  __shared__ FindSmem fs;
+  __shared__ EmitSmem es;
+  if (ws[kWsOverflow]) return;
+  EmitDst d;
+  d.n = 1;
+  d.out[0] = out;
+  emit_body(alg, cand_val, u, ws[kWsCandCount], k, kmax, d, ws, fs, es, blockIdx.x, gridDim.x,
+            cand_idx, a, (uint32_t)n);
+}
+
+// ---- the full-array passes, run only when the candidate list overflowed
+template <int PASS>
+__global__ void __launch_bounds__(kSpThreads)
+sparse_fallback_pass_kernel(const float* __restrict__ a, uint64_t n, uint32_t k,
+                            uint32_t* __restrict__ ws) {
+  __shared__ uint32_t sh[kBins];
+  __shared__ FindSmem fs;
+  if (!ws[kWsOverflow]) return;
+  pass_body<PASS>(a, n, k, ws, sh, fs, blockIdx.x, gridDim.x);
+}
+
+__global__ void __launch_bounds__(kSpThreads)
+sparse_fallback_emit_kernel(int alg, float* __restrict__ a, float* __restrict__ u, uint64_t n,
+                            uint32_t k, uint32_t kmax, uint8_t* __restrict__ out,
+                            uint32_t* __restrict__ ws) {
+  __shared__ FindSmem fs;
+  __shared__ EmitSmem es;
+  if (!ws[kWsOverflow]) return;
+  EmitDst d;
+  d.n = 1;
+  d.out[0] = out;
+  emit_body(alg, a, u, n, k, kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+}
+
 __global__ void __launch_bounds__(kSpThreads)
 sparse_scatter_kernel(const uint8_t* __restrict__ payload, float* __restrict__ out, uint64_t n,
                       uint32_t kmax, float scale, int accumulate) {
@@ -65,11 +125,19 @@ using namespace hipress;
 
 extern "C" {
 
+// minimum scratch (histograms + counters); with room for a candidate list of
+// about 8 * kmax pairs on top, the encoder reads the array once instead of three
+// times after the state update
 uint64_t hp_sparse_workspace_bytes() { return (uint64_t)kWsWords * 4; }
+uint64_t hp_sparse_workspace_bytes_for(uint64_t kmax) {
+  return (uint64_t)kWsWords * 4 + (8 * kmax + 4096) * 8;
+}
 
+// ws_bytes beyond the histogram block is used as the candidate list; when there
+// is none (the allocation-free entry point) the three full-array passes run.
 static int sparse_encode_impl(int alg, const float* g, float* a, float* u, uint64_t n, uint64_t k,
                               uint64_t kmax, float momentum, int update, uint8_t* out,
-                              uint32_t* ws, int max_ctas, cudaStream_t st) {
+                              uint32_t* ws, uint64_t ws_bytes, int max_ctas, cudaStream_t st) {
   if (n == 0 || n > 0xFFFFF000ull || k < 1 || k > n || k > kmax || kmax > 0xFFFFFFFFull)
     return HP_ERR_BAD_ARG;
   if (alg != kDgc && alg != kGradDrop) return HP_ERR_BAD_ARG;
@@ -84,10 +152,29 @@ static int sparse_encode_impl(int alg, const float* g, float* a, float* u, uint6
   if (!update) sparse_pass0_kernel<0><<<grid, kSpThreads, 0, st>>>(g, a, u, n, momentum, ws);
   else if (alg == kGradDrop) sparse_pass0_kernel<1><<<grid, kSpThreads, 0, st>>>(g, a, u, n, momentum, ws);
   else sparse_pass0_kernel<2><<<grid, kSpThreads, 0, st>>>(g, a, u, n, momentum, ws);
-  sparse_pass_kernel<1><<<grid, kSpThreads, 0, st>>>(a, n, (uint32_t)k, ws);
-  sparse_pass_kernel<2><<<grid, kSpThreads, 0, st>>>(a, n, (uint32_t)k, ws);
-  sparse_emit_kernel<<<grid, kSpThreads, 0, st>>>(alg, a, alg == kDgc ? u : nullptr, n,
-                                                   (uint32_t)k, (uint32_t)kmax, out, ws);
+  float* uu = alg == kDgc ? u : nullptr;
+  const uint64_t head = (uint64_t)kWsWords * 4;
+  const uint64_t cap = ws_bytes > head ? (ws_bytes - head) / 8 : 0;
+  if (cap >= 1024) {
+    float* cand_val = reinterpret_cast<float*>(ws + kWsWords);
+    uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + cap);
+    const int cgrid = grid < 64 ? grid : 64;
+    sparse_split_kernel<<<grid, kSpThreads, 0, st>>>(a, uu, n, (uint32_t)k, (uint32_t)kmax, out, ws,
+                                                      cand_val, cand_idx, (uint32_t)cap);
+    sparse_cand_pass_kernel<1><<<cgrid, kSpThreads, 0, st>>>(cand_val, (uint32_t)k, ws);
+    sparse_cand_pass_kernel<2><<<cgrid, kSpThreads, 0, st>>>(cand_val, (uint32_t)k, ws);
+    sparse_cand_emit_kernel<<<cgrid, kSpThreads, 0, st>>>(alg, cand_val, cand_idx, a, uu, (uint32_t)k,
+                                                          (uint32_t)kmax, out, ws, n);
+    sparse_fallback_pass_kernel<1><<<grid, kSpThreads, 0, st>>>(a, n, (uint32_t)k, ws);
+    sparse_fallback_pass_kernel<2><<<grid, kSpThreads, 0, st>>>(a, n, (uint32_t)k, ws);
+    sparse_fallback_emit_kernel<<<grid, kSpThreads, 0, st>>>(alg, a, uu, n, (uint32_t)k,
+                                                              (uint32_t)kmax, out, ws);
+  } else {
+    sparse_pass_kernel<1><<<grid, kSpThreads, 0, st>>>(a, n, (uint32_t)k, ws);
+    sparse_pass_kernel<2><<<grid, kSpThreads, 0, st>>>(a, n, (uint32_t)k, ws);
+    sparse_emit_kernel<<<grid, kSpThreads, 0, st>>>(alg, a, uu, n, (uint32_t)k, (uint32_t)kmax, out,
+                                                     ws);
+  }
   return (int)cudaGetLastError();
 }
 
@@ -95,9 +182,11 @@ static int sparse_encode_impl(int alg, const float* g, float* a, float* u, uint6
 // with g first; update=0 selects from a as it is (server / ring re-selection).
 int hp_cuda_sparse_encode(int alg, const float* g, float* a, float* u, uint64_t n, uint64_t k,
                           uint64_t kmax, float momentum, int update, uint8_t* out, void* workspace,
-                          int max_ctas, void* stream) {
+                          uint64_t workspace_bytes, int max_ctas, void* stream) {
+  if (workspace_bytes < (uint64_t)kWsWords * 4) return HP_ERR_BAD_ARG;
   return sparse_encode_impl(alg, g, a, u, n, k, kmax, momentum, update, out,
-                            static_cast<uint32_t*>(workspace), max_ctas, (cudaStream_t)stream);
+                            static_cast<uint32_t*>(workspace), workspace_bytes, max_ctas,
+                            (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -127,7 +216,7 @@ int hp_cuda_sparse_encode_noalloc(int alg, const float* g, float* a, float* u, u
     g_noalloc_ptr[dev] = static_cast<uint32_t*>(p);
   }
   return sparse_encode_impl(alg, g, a, u, n, k, kmax, momentum, update, out, g_noalloc_ptr[dev],
-                            max_ctas, (cudaStream_t)stream);
+                            (uint64_t)kWsWords * 4, max_ctas, (cudaStream_t)stream);
 }
 
 // accumulate=0: out is zero-filled first.  accumulate=1: out[idx] += val*scale.

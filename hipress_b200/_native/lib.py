@@ -123,7 +123,8 @@ def cuda():
          C.POINTER(HpComm), C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, vp)
     _sig(L.hp_sparse_workspace_bytes, C.c_uint64)
     _sig(L.hp_cuda_sparse_encode, C.c_int, C.c_int, vp, vp, vp, C.c_uint64, C.c_uint64,
-         C.c_uint64, C.c_float, C.c_int, vp, vp, C.c_int, vp)
+         C.c_uint64, C.c_float, C.c_int, vp, vp, C.c_uint64, C.c_int, vp)
+    _sig(L.hp_sparse_workspace_bytes_for, C.c_uint64, C.c_uint64)
     _sig(L.hp_cuda_sparse_decode, C.c_int, vp, vp, C.c_uint64, C.c_uint64, C.c_float, C.c_int, vp)
     _sig(L.hp_cuda_arena_alloc, C.c_int, C.c_uint64, C.POINTER(C.c_void_p))
     _sig(L.hp_cuda_arena_free, C.c_int, vp)

@@ -24,7 +24,7 @@ def main(argv=None):
     g = torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
     st = c.new_state(n, "cuda")
     pay = torch.empty(c.payload_bytes(n), dtype=torch.uint8, device="cuda")
-    ws = c.new_workspace("cuda")
+    ws = c.new_workspace("cuda", n)
     out = torch.empty(n, device="cuda")
     c.encode(g, st, out=pay, workspace=ws)
     fn = (lambda: c.encode(g, st, out=pay, workspace=ws)) if a.op == "encode" else \

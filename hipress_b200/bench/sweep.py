@@ -43,7 +43,7 @@ def sweep_ops(sizes, iters, out):
             g = torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
             st = c.new_state(n, "cuda")
             pay = torch.empty(c.payload_bytes(n), dtype=torch.uint8, device="cuda")
-            ws = c.new_workspace("cuda")
+            ws = c.new_workspace("cuda", n)
             res = torch.empty(n, device="cuda")
             enc = time_cuda(lambda: c.encode(g, st, out=pay, workspace=ws), iters=iters, flush=flush)
             dec = time_cuda(lambda: c.decode(pay, res), iters=iters, flush=flush)

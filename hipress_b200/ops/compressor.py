@@ -42,11 +42,15 @@ class Compressor:
     def new_state(self, n: int, device) -> dict:
         return {k: torch.zeros(n, dtype=torch.float32, device=device) for k in self.spec.state_names()}
 
-    def new_workspace(self, device):
-        """Scratch the sparse CUDA encoder needs (radix histograms and counters)."""
+    def new_workspace(self, device, n: int | None = None):
+        """Scratch of the sparse CUDA encoder: radix histograms and counters, plus
+        (when the tensor size ``n`` is given) room for the candidate list that lets
+        the encoder read the array once instead of three times after the update."""
         if self.spec.sparse and torch.device(device).type == "cuda":
-            return torch.zeros(int(_lib.cuda().hp_sparse_workspace_bytes()) // 4, dtype=torch.int32,
-                               device=device)
+            L = _lib.cuda()
+            nb = int(L.hp_sparse_workspace_bytes()) if n is None else \
+                int(L.hp_sparse_workspace_bytes_for(self.kmax(n)))
+            return torch.zeros((nb + 3) // 4, dtype=torch.int32, device=device)
         return None
 
     # ----------------------------------------------------------------- encode
@@ -93,13 +97,14 @@ class Compressor:
         if g.is_cuda:
             L = _lib.cuda()
             sptr = _lib.stream_ptr(stream)
-            ws = workspace if workspace is not None else self.new_workspace(g.device)
+            ws = workspace if workspace is not None else self.new_workspace(g.device, n)
             if incoming is not None:
                 # the accumulator must hold the updated local value before the merge
                 raise ValueError("merge incoming sparse payloads with decode(accumulate=True) "
                                  "after update_state(); then call encode(update=False)")
             rc = L.hp_cuda_sparse_encode(sp.alg, _c(g), _c(a), _c(u), n, k, kmax, sp.momentum,
-                                         1 if update else 0, _c(out), _c(ws), max_ctas, sptr)
+                                         1 if update else 0, _c(out), _c(ws), ws.numel() * 4, max_ctas,
+                                         sptr)
             _lib.check(rc, f"{sp.name} encode")
             return out
         L = _lib.cpu()

@@ -373,7 +373,7 @@ class GradSyncEngine:
                 sr_ptrs.append(sst["residual"].data_ptr())
             b.impl.launch_ptrs(g_ptrs, a_ptrs, u_ptrs, g_ptrs, sr_ptrs,
                                stream=b.stream or self.comm_stream)
-            self.launch_count += 10
+            self.launch_count += 19
         elif b.impl is not None:
             g_ptrs, r_ptrs, sr_ptrs, ids = [], [], [], []
             rname = "residual"

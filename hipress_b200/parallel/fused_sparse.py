@@ -34,7 +34,7 @@ def _bind():
 class FusedSparseBucket:
     """One bucket (<= 40 tensors) of a top-k algorithm on the PS topology."""
 
-    def __init__(self, spec: AlgSpec, sizes, nranks: int, rank: int, *, ctas: int = 32,
+    def __init__(self, spec: AlgSpec, sizes, nranks: int, rank: int, *, ctas: int = 0,
                  emulate: bool = False, timeout_s: float = 2.0):
         if not spec.sparse:
             raise ValueError("FusedSparseBucket handles dgc / graddrop")
@@ -122,7 +122,7 @@ def setup_engine_buckets(engine, fused_buckets) -> bool:
         return False
     from .symm import SymmetricArena
     impls = [FusedSparseBucket(engine.comp.spec, [s.n for s in b.segs], engine.N, engine.R,
-                               ctas=32, timeout_s=cfg.timeout_s) for b in fused_buckets]
+                               ctas=0, timeout_s=cfg.timeout_s) for b in fused_buckets]
     total = sum(i.region_bytes() for i in impls) + 4096
     engine.arena = SymmetricArena(total, engine.group)
     engine.status = torch.zeros(4, dtype=torch.int32, device=engine.device)

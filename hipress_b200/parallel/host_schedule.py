@@ -39,6 +39,7 @@ class HostSchedule:
         self.R = dist.get_rank(group) if dist.is_initialized() else 0
         self._bufs = {}
         self._ws = None
+        self._ws_n = 0
 
     # ---------------------------------------------------------------- helpers
     def _layout(self, segs):
@@ -83,8 +84,8 @@ class HostSchedule:
             acc = st["accum_v"] if "accum_v" in st else st["residual"]
             if incoming is not None:
                 comp.decode(incoming, acc, accumulate=True, kmax=kmax)
-            if g.is_cuda and self._ws is None:
-                self._ws = comp.new_workspace(g.device)
+            if g.is_cuda and (self._ws is None or self._ws_n < g.numel()):
+                self._ws, self._ws_n = comp.new_workspace(g.device, g.numel()), g.numel()
             comp.encode(g, st, out=out, update=True, kmax=kmax, workspace=self._ws)
         else:
             comp.encode(g, st, incoming=incoming, out=out, step=step,
@@ -163,8 +164,8 @@ class HostSchedule:
                 acc = sst["residual"] if "residual" in sst else torch.zeros(m, device=dev)
                 for q in range(N):
                     comp.decode(inbox[q][o:o + nb], acc, accumulate=True, kmax=kmax)
-                if acc.is_cuda and self._ws is None:
-                    self._ws = comp.new_workspace(dev)
+                if acc.is_cuda and (self._ws is None or self._ws_n < m):
+                    self._ws, self._ws_n = comp.new_workspace(dev, m), m
                 comp.encode(acc, {"residual": acc}, out=pull[o:o + nb], update=False, kmax=kmax,
                             workspace=self._ws)
             else:

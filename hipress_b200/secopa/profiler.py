@@ -74,7 +74,7 @@ def profile(algorithm="tbq", nnodes=8, min_elems=1 << 14, max_elems=1 << 26, ite
         g = torch.randn(n, device="cuda")
         st = comp.new_state(n, "cuda")
         pay = torch.empty(comp.payload_bytes(n), dtype=torch.uint8, device="cuda")
-        ws = comp.new_workspace("cuda")
+        ws = comp.new_workspace("cuda", n)
         out = torch.empty(n, device="cuda")
         add("encode", n, time_cuda(lambda: comp.encode(g, st, out=pay, workspace=ws), iters=iters, flush=flush))
         add("decode", n, time_cuda(lambda: comp.decode(pay, out), iters=iters, flush=flush))

@@ -43,7 +43,7 @@ def test_noalloc_matches_regular_entry_point_twice(alg_name, alg):
     torch.manual_seed(5)
     st_a = comp.new_state(n, "cuda")          # state driven through the regular entry point
     st_b = {k_: v.clone() for k_, v in st_a.items()}  # state driven through the new one
-    ws = comp.new_workspace("cuda")
+    ws = comp.new_workspace("cuda", n)
     stream = lib.stream_ptr()
     for call in range(2):                      # two calls in a row share the internal scratch
         g = torch.randn(n, device="cuda")
