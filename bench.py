@@ -177,8 +177,7 @@ def main():
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(a.steps):
-            x, y = job.to_device(*hosts[i % 4])
+        for x, y in job.stream_batches(hosts, a.steps):   # one pinned-host -> device copy per step
             lv = job.step(x, y).item()     # device -> host read of the step's loss
         e1.record()
         sync_all()

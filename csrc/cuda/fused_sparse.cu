@@ -97,7 +97,8 @@ sp_push_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_al
     return;
   } else if (STAGE == 1) {
     if (len == 0) return;
-    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, es, blockIdx.x, gridDim.x);
+    __shared__ SplitSmem sp;
+    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, sp, blockIdx.x, gridDim.x);
     return;
   } else if (STAGE == 2 || STAGE == 3) {
     if (len == 0 || ws[kWsOverflow]) return;
@@ -174,7 +175,8 @@ sp_server_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_
     return;
   } else if (STAGE == 2) {
     if (len == 0) return;
-    split_body(acc, nullptr, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, es, blockIdx.x,
+    __shared__ SplitSmem sp;
+    split_body(acc, nullptr, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, sp, blockIdx.x,
                gridDim.x);
     return;
   } else if (STAGE == 3 || STAGE == 4) {

@@ -313,90 +313,102 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
 // remaining two digit passes and the final compaction run.  One pass over the
 // array instead of three.  A candidate list that does not fit raises the
 // overflow word and the full-array passes take over.
+constexpr int kSplitBuf = 1024;  // pairs a CTA collects in shared memory per list
+
+struct SplitSmem {
+  float sel_val[kSplitBuf];
+  uint32_t sel_idx[kSplitBuf];
+  float cnd_val[kSplitBuf];
+  uint32_t cnd_idx[kSplitBuf];
+  uint32_t nsel, ncnd, base_sel, base_cnd;
+};
+
+// Selected elements are rare (about 0.1 % of the array), so a CTA collects its
+// finds in shared memory with plain shared atomics -- no block scan, no barrier
+// per tile -- and reserves its slice of the global lists once at the end.  Finds
+// beyond the shared buffer go to the global lists one by one.
 __device__ __forceinline__ void split_body(float* __restrict__ a, float* __restrict__ u, uint64_t n,
                                            uint32_t k, uint32_t kmax, const EmitDst& dst,
                                            uint32_t* __restrict__ ws, float* __restrict__ cand_val,
                                            uint32_t* __restrict__ cand_idx, uint32_t cand_cap,
-                                           FindSmem& fs, EmitSmem& es, uint32_t cta, uint32_t nctas) {
+                                           FindSmem& fs, SplitSmem& sp, uint32_t cta, uint32_t nctas) {
   uint32_t bin0, k1;
-  find_bin(ws, k, fs, bin0, k1);
+  if (threadIdx.x == 0) {
+    sp.nsel = 0;
+    sp.ncnd = 0;
+  }
+  find_bin(ws, k, fs, bin0, k1);  // contains the barriers that publish nsel / ncnd
   const size_t val_off = 16 + align_up(4ull * kmax, 16);
   const bool vec = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(u)) & 15) == 0;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint64_t tiles = (n + 4095) / 4096;
   for (uint64_t t = cta; t < tiles; t += nctas) {
-    float e[16];
-    uint32_t flag = 0;  // 2 bits per element: bit0 above the bin, bit1 inside it
-    uint32_t cnt = 0;   // low 16: above, high 16: inside
+    float4 av[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      av[j] = ld4(a, t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4, n, vec);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint64_t i = t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4;
-      const float4 av = ld4(a, i, n, vec);
-      e[4 * j] = av.x; e[4 * j + 1] = av.y; e[4 * j + 2] = av.z; e[4 * j + 3] = av.w;
+      const float e[4] = {av[j].x, av[j].y, av[j].z, av[j].w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint32_t bin = abs_key(e[4 * j + q]) >> 19;
-        if (i + q < n) {
-          if (bin > bin0) { flag |= 1u << (2 * (4 * j + q)); cnt += 1u; }
-          else if (bin == bin0) { flag |= 2u << (2 * (4 * j + q)); cnt += 1u << 16; }
-        }
-      }
-    }
-    uint32_t inc = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += y;
-    }
-    if (lane == 31) es.warp_tot[warp] = inc;
-    __syncthreads();
-    uint32_t wbase = 0, tot = 0;
-#pragma unroll
-    for (int w = 0; w < kSpThreads / 32; ++w) {
-      const uint32_t wt = es.warp_tot[w];
-      if (w < warp) wbase += wt;
-      tot += wt;
-    }
-    const uint32_t excl = wbase + inc - cnt;
-    if (tot == 0) {
-      __syncthreads();
-      continue;
-    }
-    const uint32_t tot_gt = tot & 0xFFFFu, tot_in = tot >> 16;
-    if (threadIdx.x == 0) {
-      es.base_gt = tot_gt ? atomicAdd(ws + kWsOutCount, tot_gt) : 0u;
-      es.base_eq = tot_in ? atomicAdd(ws + kWsCandCount, tot_in) : 0u;
-      if (tot_in && es.base_eq + tot_in > cand_cap) ws[kWsOverflow] = 1u;
-    }
-    __syncthreads();
-    uint32_t pg = es.base_gt + (excl & 0xFFFFu);
-    uint32_t pc = es.base_eq + (excl >> 16);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint64_t i = t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t f = (flag >> (2 * (4 * j + q))) & 3u;
-        if (f & 1u) {
-          const uint32_t pos = pg++;
-          if (pos < kmax) {
-            for (int d = 0; d < dst.n; ++d) {
-              reinterpret_cast<uint32_t*>(dst.out[d] + 16)[pos] = (uint32_t)(i + q);
-              reinterpret_cast<float*>(dst.out[d] + val_off)[pos] = e[4 * j + q];
+        const uint32_t bin = abs_key(e[q]) >> 19;
+        if (i + q >= n || bin < bin0) continue;
+        if (bin > bin0) {  // certainly among the k largest: send and zero now
+          const uint32_t p = atomicAdd(&sp.nsel, 1u);
+          if (p < (uint32_t)kSplitBuf) {
+            sp.sel_val[p] = e[q];
+            sp.sel_idx[p] = (uint32_t)(i + q);
+          } else {
+            const uint32_t pos = atomicAdd(ws + kWsOutCount, 1u);
+            if (pos < kmax)
+              for (int d = 0; d < dst.n; ++d) {
+                reinterpret_cast<uint32_t*>(dst.out[d] + 16)[pos] = (uint32_t)(i + q);
+                reinterpret_cast<float*>(dst.out[d] + val_off)[pos] = e[q];
+              }
+          }
+          a[i + q] = 0.0f;
+          if (u) u[i + q] = 0.0f;
+        } else {           // inside the threshold bin: decided on the candidate list
+          const uint32_t p = atomicAdd(&sp.ncnd, 1u);
+          if (p < (uint32_t)kSplitBuf) {
+            sp.cnd_val[p] = e[q];
+            sp.cnd_idx[p] = (uint32_t)(i + q);
+          } else {
+            const uint32_t pos = atomicAdd(ws + kWsCandCount, 1u);
+            if (pos < cand_cap) {
+              cand_val[pos] = e[q];
+              cand_idx[pos] = (uint32_t)(i + q);
+            } else {
+              ws[kWsOverflow] = 1u;
             }
-            a[i + q] = 0.0f;
-            if (u) u[i + q] = 0.0f;
-          }
-        } else if (f & 2u) {
-          const uint32_t pos = pc++;
-          if (pos < cand_cap) {
-            cand_val[pos] = e[4 * j + q];
-            cand_idx[pos] = (uint32_t)(i + q);
           }
         }
       }
     }
-    __syncthreads();
+  }
+  __syncthreads();
+  const uint32_t nsel = min(sp.nsel, (uint32_t)kSplitBuf), ncnd = min(sp.ncnd, (uint32_t)kSplitBuf);
+  if (threadIdx.x == 0) {
+    sp.base_sel = nsel ? atomicAdd(ws + kWsOutCount, nsel) : 0u;
+    sp.base_cnd = ncnd ? atomicAdd(ws + kWsCandCount, ncnd) : 0u;
+    if (ncnd && sp.base_cnd + ncnd > cand_cap) ws[kWsOverflow] = 1u;
+  }
+  __syncthreads();
+  for (uint32_t p = threadIdx.x; p < nsel; p += kSpThreads) {
+    const uint32_t pos = sp.base_sel + p;
+    if (pos < kmax)
+      for (int d = 0; d < dst.n; ++d) {
+        reinterpret_cast<uint32_t*>(dst.out[d] + 16)[pos] = sp.sel_idx[p];
+        reinterpret_cast<float*>(dst.out[d] + val_off)[pos] = sp.sel_val[p];
+      }
+  }
+  for (uint32_t p = threadIdx.x; p < ncnd; p += kSpThreads) {
+    const uint32_t pos = sp.base_cnd + p;
+    if (pos < cand_cap) {
+      cand_val[pos] = sp.cnd_val[p];
+      cand_idx[pos] = sp.cnd_idx[p];
+    }
   }
 }
 

@@ -59,11 +59,11 @@ sparse_split_kernel(float* __restrict__ a, float* __restrict__ u, uint64_t n, ui
                     uint32_t kmax, uint8_t* __restrict__ out, uint32_t* __restrict__ ws,
                     float* __restrict__ cand_val, uint32_t* __restrict__ cand_idx, uint32_t cap) {
   __shared__ FindSmem fs;
-  __shared__ EmitSmem es;
+  __shared__ SplitSmem sp;
   EmitDst d;
   d.n = 1;
   d.out[0] = out;
-  split_body(a, u, n, k, kmax, d, ws, cand_val, cand_idx, cap, fs, es, blockIdx.x, gridDim.x);
+  split_body(a, u, n, k, kmax, d, ws, cand_val, cand_idx, cap, fs, sp, blockIdx.x, gridDim.x);
 }
 
 template <int PASS>

@@ -61,6 +61,33 @@ class Job:
             x = x.contiguous(memory_format=torch.channels_last)
         return x, y
 
+    def stream_batches(self, hosts, count: int):
+        """Yields `count` device batches, copying batch i+1 from pinned host memory on
+        a side stream while step i computes (one host-to-device copy per step)."""
+        if self.device.type != "cuda":
+            for i in range(count):
+                yield self.to_device(*hosts[i % len(hosts)])
+            return
+        side = torch.cuda.Stream()
+
+        def issue(i):
+            with torch.cuda.stream(side):
+                x, y = self.to_device(*hosts[i % len(hosts)])
+                ev = torch.cuda.Event()
+                ev.record(side)
+            return x, y, ev
+
+        nxt = issue(0)
+        for i in range(count):
+            x, y, ev = nxt
+            if i + 1 < count:
+                nxt = issue(i + 1)
+            cur = torch.cuda.current_stream()
+            cur.wait_event(ev)
+            x.record_stream(cur)
+            y.record_stream(cur)
+            yield x, y
+
     def h2d_bytes(self, x, y):
         return x.numel() * x.element_size() + y.numel() * y.element_size()
 

@@ -53,8 +53,7 @@ def main(argv=None):
         if cuda:
             torch.cuda.synchronize()
         t0 = time.time()
-        for it in range(a.num_iterations):
-            x, y = job.to_device(*hosts[it % 4])
+        for it, (x, y) in enumerate(job.stream_batches(hosts, a.num_iterations)):
             loss = job.step(x, y)
             step += 1
             if it % 10 == 9 or it == a.num_iterations - 1:
