@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--comprplan", default=None)
     ap.add_argument("--sync-backend", default="auto", choices=["auto", "fused", "host", "allreduce"])
     ap.add_argument("--ctas", type=int, default=None)
+    ap.add_argument("--bucket-mb", type=int, default=None)
     ap.add_argument("--partition-sms", type=int, default=None)
     ap.add_argument("--partition-ctas", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
@@ -129,6 +130,8 @@ def main():
                 comp_threshold=a.comp_threshold, plan=a.comprplan, backend=a.sync_backend)
     if a.ctas:
         over["ctas"] = a.ctas
+    if a.bucket_mb:
+        over["bucket_bytes"] = a.bucket_mb << 20
     if a.partition_sms is not None:
         over["partition_sms"] = a.partition_sms
     if a.partition_ctas:
@@ -177,8 +180,22 @@ def main():
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for x, y in job.stream_batches(hosts, a.steps):   # one pinned-host -> device copy per step
-            lv = job.step(x, y).item()     # device -> host read of the step's loss
+        # every step: one pinned-host -> device copy of its inputs and one device ->
+        # host copy of its loss; the loss of step i is read on the host while step
+        # i+1 is already queued, so the host never stalls the launch stream
+        loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+        loss_ev = [torch.cuda.Event(), torch.cuda.Event()]
+        losses = []
+        for i, (x, y) in enumerate(job.stream_batches(hosts, a.steps)):
+            out = job.step(x, y)
+            loss_host[i & 1].copy_(out, non_blocking=True)
+            loss_ev[i & 1].record()
+            if i > 0:
+                loss_ev[(i - 1) & 1].synchronize()
+                losses.append(float(loss_host[(i - 1) & 1]))
+        loss_ev[(a.steps - 1) & 1].synchronize()
+        losses.append(float(loss_host[(a.steps - 1) & 1]))
+        lv = losses[-1]
         e1.record()
         sync_all()
         t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)

@@ -128,11 +128,12 @@ int hp_cpu_dense_encode(int alg, int bits, const float* g, float* r,
       meta[2 * t] = mn;
       meta[2 * t + 1] = mx;
       const float gap = tern_gap(mn, mx, bits);
+      const float inv_gap = tern_inv_gap(gap);
       for (uint64_t i = 0; i < m; ++i) {
         const uint64_t ge = elem_offset + t0 + i;
         Philox4 rnd = philox4x32_10((uint32_t)(ge >> 2), tensor_id, step, salt,
                                     (uint32_t)seed, (uint32_t)(seed >> 32));
-        uint32_t c = tern_code(x[i], mn, gap, u01(rnd.v[ge & 3]), bits);
+        uint32_t c = tern_code(x[i], mn, inv_gap, u01(rnd.v[ge & 3]), bits);
         put_code(codes, t0 + i, bits, c);
         if (r) r[t0 + i] = x[i] - tern_value(c, mn, gap);
       }

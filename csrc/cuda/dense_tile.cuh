@@ -193,8 +193,11 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
     meta[0] = mn;
     meta[1] = mx;
   }
-  float gap = 0.0f;
-  if (ALG == kTernGrad) gap = tern_gap(meta[0], meta[1], B);
+  float gap = 0.0f, inv_gap = 0.0f;
+  if (ALG == kTernGrad) {
+    gap = tern_gap(meta[0], meta[1], B);
+    inv_gap = tern_inv_gap(gap);
+  }
 #pragma unroll
   for (int j = 0; j < kIter; ++j) {
     const int i0 = 4 * (j * kThreads + (int)threadIdx.x);
@@ -216,7 +219,7 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
           c = tbq_code(x[j][e], P.tau);
           d = tbq_value(c, P.tau);
         } else {
-          c = tern_code(x[j][e], meta[0], gap, u01(rnd.v[e]), B);
+          c = tern_code(x[j][e], meta[0], inv_gap, u01(rnd.v[e]), B);
           d = tern_value(c, meta[0], gap);
         }
         f |= c << (e * B);

@@ -567,9 +567,15 @@ static int launch_fused(int topo, const BucketDev& bk, const HpComm& cm, const F
   void (*kern)(const BucketDev, const HpComm, const FusedParams) =
       topo == HP_TOPO_RING ? ring_dense_kernel<ALG, B> : ps_dense_kernel<ALG, B>;
   const size_t smem = sizeof(FusedSmem);
-  cudaError_t e0 = cudaFuncSetAttribute((const void*)kern,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e0 != cudaSuccess) return (int)e0;
+  static bool attr_set[2][64] = {};  // per (topology, device): the attribute is sticky
+  int cur_dev = 0;
+  cudaGetDevice(&cur_dev);
+  if (cur_dev < 0 || cur_dev >= 64 || !attr_set[topo][cur_dev]) {
+    cudaError_t e0 = cudaFuncSetAttribute((const void*)kern,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e0 != cudaSuccess) return (int)e0;
+    if (cur_dev >= 0 && cur_dev < 64) attr_set[topo][cur_dev] = true;
+  }
   if (cm.emulate) {
     int dev = 0, sms = 0, per_sm = 0;
     cudaError_t e = cudaGetDevice(&dev);

@@ -147,9 +147,12 @@ HP_HD float onebit_value(uint32_t code, float s) { return code ? -s : s; }
 HP_HD float tern_gap(float mn, float mx, int bits) {
   return (mx - mn) / (float)((1u << bits) - 1u);
 }
-HP_HD uint32_t tern_code(float x, float mn, float gap, float u, int bits) {
-  if (!(gap > 0.0f)) return 0u;
-  float q = floorf((x - mn) / gap + u);
+// inv_gap = 1 / gap, computed once per tile (a multiply per element instead of a
+// division; both implementations round the same way)
+HP_HD float tern_inv_gap(float gap) { return gap > 0.0f ? 1.0f / gap : 0.0f; }
+HP_HD uint32_t tern_code(float x, float mn, float inv_gap, float u, int bits) {
+  if (!(inv_gap > 0.0f)) return 0u;
+  float q = floorf((x - mn) * inv_gap + u);
   float qmax = (float)((1u << bits) - 1u);
   if (!(q > 0.0f)) q = 0.0f;   // also catches NaN
   if (q > qmax) q = qmax;

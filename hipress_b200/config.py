@@ -22,7 +22,7 @@ class HipressConfig:
     momentum: float = 0.9             # dgc momentum correction
     seed: int = 0
     backend: str = "auto"             # auto | fused | host | allreduce
-    bucket_bytes: int = 64 << 20      # gradient bytes per fused launch
+    bucket_bytes: int = 256 << 20     # gradient bytes per fused launch
     plain_bucket_bytes: int = 32 << 20
     ctas: int = 296                   # CTAs of a fused kernel that runs on the whole GPU
     partition_sms: int = 0            # SMs reserved (green context) for fused kernels that overlap backward; 0 = off

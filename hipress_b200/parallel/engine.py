@@ -146,6 +146,7 @@ class GradSyncEngine:
         self.launch_count = 0
         self.bytes_sent = 0
         self.timeline = Timeline()
+        self._events = [torch.cuda.Event() for _ in self.buckets] if self.on_cuda else []
 
     # ------------------------------------------------------------------ plan
     def _make_entries(self, named):
@@ -336,6 +337,19 @@ class GradSyncEngine:
 
     def _launch(self, b: Bucket):
         b.launched = True
+        if self.on_cuda and b.fused and b.impl is not None:
+            # fused kernels take the raw stream: no stream context switch on the
+            # autograd thread, which is busy launching backward
+            st = b.stream or self.comm_stream
+            ev = self._events[b.index]
+            ev.record()
+            st.wait_event(ev)
+            tok = self.timeline.begin(f"bucket{b.index}", st) if self.timeline.enabled else None
+            self._launch_fused(b)
+            if tok is not None:
+                self.timeline.end(tok, st, step=self.step_no, fused=True,
+                                  elems=sum(e.numel for e in b.entries))
+            return
         if self.on_cuda:
             st = b.stream or self.comm_stream
             ev = torch.cuda.Event()
