@@ -60,38 +60,133 @@ struct FusedParams {
   float inv_n;
 };
 
-// decode tile t of the payload at `base` and add it to x (or assign when !add)
+// ------------------------------------------------------------------ transport
+// Payloads travel in 8-byte slots {32 bits of codes, 32-bit epoch}: one aligned
+// 8-byte store is delivered whole, so the receiver polls the slot itself until
+// the epoch of this launch shows up.  No separate flag, no system-scope fence and
+// no CTA barrier per hop; the cost is 2x on payload bytes that are 16-32x smaller
+// than the gradient to begin with.  Slots are never reused inside a launch and the
+// epoch grows with every launch, so stale contents can never match.
+//
+// Per tile: [META slots (scale / min,max as raw bits)] [W * 256 code slots], where
+// thread t owns code slots w*256 + t and W = 32-bit words of codes per thread.
+template <int B>
+struct LL {
+  static constexpr int W = B <= 2 ? 1 : B / 2;
+};
+template <int ALG>
+struct MetaOf {
+  static constexpr int N = ALG == kOnebit ? 1 : (ALG == kTernGrad ? 2 : 0);
+};
 template <int ALG, int B>
-__device__ __forceinline__ void decode_into(const uint8_t* base, uint32_t chunk, uint32_t t, int m,
-                                            float tau, bool add, float (&x)[kIter][4]) {
-  PayloadView v = payload_view(const_cast<uint8_t*>(base), ALG, chunk);
-  float meta[2];
-  load_meta<ALG>(v.meta, t, meta);
-  const uint8_t* tc = v.codes + (size_t)t * (kTile * B / 8);
+__device__ __forceinline__ constexpr int tile_slots() {
+  return MetaOf<ALG>::N + LL<B>::W * kThreads;
+}
+
+__device__ __forceinline__ void ll_store(uint2* slot, uint32_t data, uint32_t epoch) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(slot), "r"(data), "r"(epoch)
+               : "memory");
+}
+__device__ __forceinline__ uint2 ll_load(const uint2* slot) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(slot)
+               : "memory");
+  return v;
+}
+
+// Spin (bounded) until the slot carries this launch's epoch.  `v` holds a first
+// load issued earlier so that several slots can be in flight before any spinning.
+__device__ __forceinline__ uint32_t ll_finish(const uint2* slot, uint2 v, const HpComm& cm,
+                                              uint32_t* status, uint32_t code, WaitState& ws) {
+  if (v.y == cm.epoch) return v.x;
+  volatile int* poisoned = &ws.poisoned;
+  if (*poisoned) return v.x;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    v = ll_load(slot);
+    if (v.y == cm.epoch) break;
+    if ((++polls & 63u) == 0 && (*poisoned || global_timer_ns() - t0 > cm.timeout_ns)) {
+      atomicCAS(status, 0u, code);
+      *poisoned = 1;
+      break;
+    }
+  }
+  return v.x;
+}
+
+template <int B>
+__device__ __forceinline__ void pack_words(const uint32_t (&f)[kIter], uint32_t (&w)[LL<B>::W]) {
+  if (B == 1) w[0] = f[0] | (f[1] << 4) | (f[2] << 8) | (f[3] << 12);
+  else if (B == 2) w[0] = f[0] | (f[1] << 8) | (f[2] << 16) | (f[3] << 24);
+  else if (B == 4) { w[0] = f[0] | (f[1] << 16); w[LL<B>::W - 1] = f[2] | (f[3] << 16); }
+  else {
 #pragma unroll
-  for (int j = 0; j < kIter; ++j) {
-    float d[4];
-    decode_frag<ALG, B>(load_frag<B>(tc, j, m), meta, tau, d);
+    for (int j = 0; j < kIter; ++j) w[j % LL<B>::W] = f[j];
+  }
+}
+template <int B>
+__device__ __forceinline__ void unpack_words(const uint32_t (&w)[LL<B>::W], uint32_t (&f)[kIter]) {
+  if (B == 1) { f[0] = w[0] & 15u; f[1] = (w[0] >> 4) & 15u; f[2] = (w[0] >> 8) & 15u; f[3] = (w[0] >> 12) & 15u; }
+  else if (B == 2) { f[0] = w[0] & 255u; f[1] = (w[0] >> 8) & 255u; f[2] = (w[0] >> 16) & 255u; f[3] = w[0] >> 24; }
+  else if (B == 4) { f[0] = w[0] & 0xFFFFu; f[1] = w[0] >> 16; f[2] = w[LL<B>::W - 1] & 0xFFFFu; f[3] = w[LL<B>::W - 1] >> 16; }
+  else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) x[j][e] = add ? x[j][e] + d[e] : d[e];
+    for (int j = 0; j < kIter; ++j) f[j] = w[j % LL<B>::W];
   }
 }
 
-// store staged codes + metadata (+ header for tile 0) of tile t into a payload
+// slots of tile t inside the payload that starts at `base`
 template <int ALG, int B>
-__device__ __forceinline__ void store_payload_tile(uint8_t* base, uint32_t chunk, uint32_t t, int m,
-                                                   uint32_t n_valid, const float (&meta)[2],
-                                                   float tau, const TileSmem& s) {
-  PayloadView v = payload_view(base, ALG, chunk);
-  copy_codes(v.codes + (size_t)t * (kTile * B / 8), s.codes, tile_code_bytes(m, B));
+__device__ __forceinline__ uint2* tile_base(uint8_t* base, uint32_t t) {
+  return reinterpret_cast<uint2*>(base) + (size_t)t * tile_slots<ALG, B>();
+}
+
+// send one encoded tile: this thread's code words, and (thread 0) the metadata
+template <int ALG, int B>
+__device__ __forceinline__ void send_tile(uint8_t* base, uint32_t t, const uint32_t (&w)[LL<B>::W],
+                                          const float (&meta)[2], uint32_t epoch) {
+  uint2* tb = tile_base<ALG, B>(base, t);
   if (threadIdx.x == 0) {
-    if (ALG == kOnebit) v.meta[t] = meta[0];
-    if (ALG == kTernGrad) {
-      v.meta[2 * t] = meta[0];
-      v.meta[2 * t + 1] = meta[1];
-    }
-    if (t == 0) write_header(base, n_valid, ALG, B, tau);
+#pragma unroll
+    for (int k = 0; k < MetaOf<ALG>::N; ++k) ll_store(tb + k, __float_as_uint(meta[k]), epoch);
   }
+#pragma unroll
+  for (int k = 0; k < LL<B>::W; ++k)
+    ll_store(tb + MetaOf<ALG>::N + k * kThreads + threadIdx.x, w[k], epoch);
+}
+
+// first (non-blocking) loads of a tile's slots
+template <int ALG, int B>
+struct TileRx {
+  uint2 w[LL<B>::W];
+  uint2 m[MetaOf<ALG>::N > 0 ? MetaOf<ALG>::N : 1];
+};
+template <int ALG, int B>
+__device__ __forceinline__ void recv_issue(const uint8_t* base, uint32_t t, TileRx<ALG, B>& rx) {
+  const uint2* tb = tile_base<ALG, B>(const_cast<uint8_t*>(base), t);
+#pragma unroll
+  for (int k = 0; k < MetaOf<ALG>::N; ++k) rx.m[k] = ll_load(tb + k);
+#pragma unroll
+  for (int k = 0; k < LL<B>::W; ++k) rx.w[k] = ll_load(tb + MetaOf<ALG>::N + k * kThreads + threadIdx.x);
+}
+// wait for whatever was not there yet, then decode into d[j][e]
+template <int ALG, int B>
+__device__ __forceinline__ void recv_finish(const uint8_t* base, uint32_t t, TileRx<ALG, B>& rx,
+                                            const HpComm& cm, uint32_t* status, uint32_t code,
+                                            WaitState& ws, float tau, float (&d)[kIter][4]) {
+  const uint2* tb = tile_base<ALG, B>(const_cast<uint8_t*>(base), t);
+  float meta[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int k = 0; k < MetaOf<ALG>::N; ++k)
+    meta[k] = __uint_as_float(ll_finish(tb + k, rx.m[k], cm, status, code, ws));
+  uint32_t w[LL<B>::W], f[kIter];
+#pragma unroll
+  for (int k = 0; k < LL<B>::W; ++k)
+    w[k] = ll_finish(tb + MetaOf<ALG>::N + k * kThreads + threadIdx.x, rx.w[k], cm, status, code, ws);
+  unpack_words<B>(w, f);
+#pragma unroll
+  for (int j = 0; j < kIter; ++j) decode_frag<ALG, B>(f[j], meta, tau, d[j]);
 }
 
 __device__ __forceinline__ uint32_t chunk_valid(uint32_t n, uint32_t chunk, int c) {
@@ -222,7 +317,6 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
   const int G = (int)gridDim.x;
   const int b = (int)blockIdx.x;
   uint8_t* my_inbox = reinterpret_cast<uint8_t*>(cm.inbox[R]);
-  uint32_t* my_flags = reinterpret_cast<uint32_t*>(cm.flags[R]);
   // prefetcher state: runs ahead of the consumer over the same tile sequence
   Cursor prod;
   cursor_begin(bk, G, b, 0, phase_spec<TOPO>(0, N, R).chunk, prod);
@@ -246,7 +340,6 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
                                 : nullptr;
     const uint8_t* in_base =
         ps.in_slot >= 0 ? my_inbox + (size_t)ps.in_slot * bk.slot_bytes : nullptr;
-    bool waited = ps.in_slot < 0;
     TileRef tr;
     while (cursor_next(bk, G, b, cons, tr)) {
       const SegDev& sg = bk.seg[tr.seg];
@@ -287,27 +380,14 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
           pg += kTile;
           if (prr) prr += kTile;
         }
-        if (!waited) {  // the incoming payload is needed only now; g and r are already in flight
-          wait_flag(my_flags + (size_t)ps.in_slot * G + b, cm.epoch, cm.timeout_ns, status,
-                    HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
-                    sm.ws);
-          waited = true;
-        }
         const int m = tile_valid(tr, u);
         const uint32_t t = tr.t0 + u;
         const float* gp = gp0 + (size_t)u * kTile;
         float* rp = rp0 ? rp0 + (size_t)u * kTile : nullptr;
         float x[kIter][4];
-        // loads of the incoming payload go out before anything waits
-        uint32_t ifr[kIter];
-        float imeta[2];
-        if (in_base) {
-          PayloadView iv = payload_view(const_cast<uint8_t*>(in_base + sg.pay_off), ALG, sg.chunk);
-          load_meta<ALG>(iv.meta, t, imeta);
-          const uint8_t* tc = iv.codes + (size_t)t * (kTile * B / 8);
-#pragma unroll
-          for (int j = 0; j < kIter; ++j) ifr[j] = load_frag<B>(tc, j, m);
-        }
+        // first loads of the incoming payload go out before anything waits
+        TileRx<ALG, B> rx;
+        if (in_base) recv_issue<ALG, B>(in_base + sg.pay_off, t, rx);
         const bool bulk = aligned && m == kTile;
         int st = 0;
         if (bulk) {
@@ -322,13 +402,14 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
           load_tile(gp, m, x);
         }
         if (in_base) {
+          float d[kIter][4];
+          recv_finish<ALG, B>(in_base + sg.pay_off, t, rx, cm, status,
+                              HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
+                              sm.ws, fp.P.tau, d);
 #pragma unroll
-          for (int j = 0; j < kIter; ++j) {
-            float d[4];
-            decode_frag<ALG, B>(ifr[j], imeta, fp.P.tau, d);
+          for (int j = 0; j < kIter; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] + d[e];
-          }
+            for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] + d[j][e];
         }
         if (rp) {
           float rr[kIter][4];
@@ -344,76 +425,47 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
         encode_tile<ALG, B>(x, m, fp.P, sg.id, tr.off0 + (size_t)u * kTile, fp.P.salt + ps.salt,
                             sm.tile, meta, frag);
         if (rp) store_tile(rp, m, x);
-        stage_frags<B>(sm.tile.codes, frag);
-        __syncthreads();
+        uint32_t words[LL<B>::W];
+        pack_words<B>(frag, words);
 #pragma unroll
         for (int q = 0; q < HP_MAX_RANKS; ++q)
-          if (q < ps.ndst)
-            store_payload_tile<ALG, B>(dst_base[q] + sg.pay_off, sg.chunk, t, m, tr.nv, meta,
-                                       fp.P.tau, sm.tile);
-        __syncthreads();
+          if (q < ps.ndst) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, cm.epoch);
+        __syncthreads();  // the prefetch stage of this tile may be refilled from here on
       }
-    }
-    if (!waited)  // no tile in this phase, the flag protocol still runs
-      wait_flag(my_flags + (size_t)ps.in_slot * G + b, cm.epoch, cm.timeout_ns, status,
-                HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255), sm.ws);
-    // publish: everything this CTA stored for this phase is complete
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      for (int q = 0; q < ps.ndst; ++q)
-        st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(ps.dst0 + q) % N]) +
-                           (size_t)ps.dst_slot * G + b,
-                       cm.epoch);
     }
   }
 }
 
-// decode the reduced chunk `c` that arrived in inbox slot `slot` into the gradient
+// decode the reduced chunk `c` that arrives in inbox slot `slot` into the gradient
 template <int ALG, int B>
 __device__ __forceinline__ void decode_phase(const BucketDev& bk, const HpComm& cm,
                                              const FusedParams& fp, FusedSmem& sm, int R, int E,
                                              int slot, int c, uint32_t* status) {
   const int G = (int)gridDim.x;
   const int b = (int)blockIdx.x;
-  uint8_t* my_inbox = reinterpret_cast<uint8_t*>(cm.inbox[R]);
-  uint32_t* my_flags = reinterpret_cast<uint32_t*>(cm.flags[R]);
-  wait_flag(my_flags + (size_t)slot * G + b, cm.epoch, cm.timeout_ns, status,
-            HP_STATUS_TIMEOUT | (2u << 16) | ((uint32_t)slot << 8) | (b & 255), sm.ws);
-  const uint8_t* sp = my_inbox + (size_t)slot * bk.slot_bytes;
+  const uint8_t* sp = reinterpret_cast<const uint8_t*>(cm.inbox[R]) + (size_t)slot * bk.slot_bytes;
+  const uint32_t code = HP_STATUS_TIMEOUT | (2u << 16) | ((uint32_t)slot << 8) | (b & 255);
   Cursor cur;
   cursor_begin(bk, G, b, 0, c, cur);
   TileRef tr;
   while (cursor_next(bk, G, b, cur, tr)) {
     const SegDev& sg = bk.seg[tr.seg];
     float* op = sg.out + E * cm.emu_stride_out + tr.off0;
-    PayloadView v = payload_view(const_cast<uint8_t*>(sp + sg.pay_off), ALG, sg.chunk);
-    // issue every payload load of the super-tile first, then decode and store:
-    // one exposed L2 round trip per kSuper tiles instead of one per tile
-    uint32_t fr[kSuper][kIter];
-    float mt[kSuper][2];
+    // first loads of the whole super-tile go out before anything spins
+    TileRx<ALG, B> rx[kSuper];
 #pragma unroll
-    for (uint32_t u = 0; u < (uint32_t)kSuper; ++u) {
-      if (u < tr.cnt) {
-        const int m = tile_valid(tr, u);
-        load_meta<ALG>(v.meta, tr.t0 + u, mt[u]);
-        const uint8_t* tc = v.codes + (size_t)(tr.t0 + u) * (kTile * B / 8);
-#pragma unroll
-        for (int j = 0; j < kIter; ++j) fr[u][j] = load_frag<B>(tc, j, m);
-      }
-    }
+    for (uint32_t u = 0; u < (uint32_t)kSuper; ++u)
+      if (u < tr.cnt) recv_issue<ALG, B>(sp + sg.pay_off, tr.t0 + u, rx[u]);
 #pragma unroll
     for (uint32_t u = 0; u < (uint32_t)kSuper; ++u) {
       if (u < tr.cnt) {
         const int m = tile_valid(tr, u);
         float x[kIter][4];
+        recv_finish<ALG, B>(sp + sg.pay_off, tr.t0 + u, rx[u], cm, status, code, sm.ws, fp.P.tau, x);
 #pragma unroll
-        for (int j = 0; j < kIter; ++j) {
-          float d[4];
-          decode_frag<ALG, B>(fr[u][j], mt[u], fp.P.tau, d);
+        for (int j = 0; j < kIter; ++j)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) x[j][e] = d[e] * fp.inv_n;
-        }
+          for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] * fp.inv_n;
         store_tile(op + (size_t)u * kTile, m, x);
       }
     }
@@ -462,20 +514,22 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   const int b = (int)blockIdx.x;
   uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   uint8_t* my_inbox = reinterpret_cast<uint8_t*>(cm.inbox[R]);
-  uint32_t* my_flags = reinterpret_cast<uint32_t*>(cm.flags[R]);
   fused_prologue(sm);
 
   // phase 1: push
   encode_phases<ALG, B, HP_TOPO_PS>(bk, cm, fp, sm, R, E, status);
 
   // phase 2: server for chunk R: sum the N payloads in rank order, re-encode, broadcast
-  for (int q = 0; q < N; ++q)
-    wait_flag(my_flags + (size_t)q * G + b, cm.epoch, cm.timeout_ns, status,
-              HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)q << 8) | (b & 255), sm.ws);
   {
     Cursor cur;
     cursor_begin(bk, G, b, 0, R, cur);
     TileRef tr;
+    uint8_t* dst_base[HP_MAX_RANKS];
+#pragma unroll
+    for (int q = 0; q < HP_MAX_RANKS; ++q)
+      dst_base[q] = q < N ? reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) +
+                                (size_t)(N + R) * bk.slot_bytes
+                          : nullptr;
     while (cursor_next(bk, G, b, cur, tr)) {
       const SegDev& sg = bk.seg[tr.seg];
       for (uint32_t u = 0; u < tr.cnt; ++u) {
@@ -483,9 +537,23 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
         const uint32_t t = tr.t0 + u;
         const size_t coff = (size_t)t * kTile;  // offset inside the owned chunk
         float x[kIter][4];
-        for (int q = 0; q < N; ++q)
-          decode_into<ALG, B>(my_inbox + (size_t)q * bk.slot_bytes + sg.pay_off, sg.chunk, t, m,
-                              fp.P.tau, q > 0, x);
+        // the N pushes are polled two at a time: loads of the next source are in
+        // flight while the current one is decoded
+        TileRx<ALG, B> rx[2];
+        recv_issue<ALG, B>(my_inbox + sg.pay_off, t, rx[0]);
+        for (int q = 0; q < N; ++q) {
+          if (q + 1 < N)
+            recv_issue<ALG, B>(my_inbox + (size_t)(q + 1) * bk.slot_bytes + sg.pay_off, t,
+                               rx[(q + 1) & 1]);
+          float d[kIter][4];
+          recv_finish<ALG, B>(my_inbox + (size_t)q * bk.slot_bytes + sg.pay_off, t, rx[q & 1], cm,
+                              status, HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)q << 8) | (b & 255),
+                              sm.ws, fp.P.tau, d);
+#pragma unroll
+          for (int j = 0; j < kIter; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[j][e] = q > 0 ? x[j][e] + d[j][e] : d[j][e];
+        }
         float* rp = sg.sr ? sg.sr + E * cm.emu_stride_sr + coff : nullptr;
         if (rp) {
           float rr[kIter][4];
@@ -500,23 +568,13 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
         encode_tile<ALG, B>(x, m, fp.P, sg.id, (size_t)R * sg.chunk + coff,
                             fp.P.salt + (uint32_t)(R * 256 + 1), s, meta, frag);
         if (rp) store_tile(rp, m, x);
-        stage_frags<B>(s.codes, frag);
-        __syncthreads();
-        for (int q = 0; q < N; ++q) {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) +
-                         (size_t)(N + R) * bk.slot_bytes + sg.pay_off;
-          store_payload_tile<ALG, B>(dst, sg.chunk, t, m, tr.nv, meta, fp.P.tau, s);
-        }
-        __syncthreads();
+        uint32_t words[LL<B>::W];
+        pack_words<B>(frag, words);
+#pragma unroll
+        for (int q = 0; q < HP_MAX_RANKS; ++q)
+          if (q < N) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, cm.epoch);
       }
     }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    for (int q = 0; q < N; ++q)
-      st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + q) % N]) + (size_t)(N + R) * G + b,
-                     cm.epoch);
   }
 
   // phase 3: pull: decode every owner's reduced chunk
@@ -548,7 +606,11 @@ static int build_bucket(int alg, int bits, const HpSeg* segs, int nseg, int nran
     d.pay_off = (uint32_t)pay;
     d.id = segs[i].id;
     tiles += (d.tiles + kSuper - 1) / kSuper;
-    pay += align_up(dense_payload_bytes(alg, bits, chunk), 128);
+    {
+      const uint64_t words = bits <= 2 ? 1 : bits / 2;
+      const uint64_t slots = dense_meta_floats(alg) + words * kThreads;  // per tile
+      pay += align_up((chunk / kTile) * slots * 8, 128);
+    }
     if (pay > 0xFFFFFFFFull || tiles > 0x7FFFFFFFull) return HP_ERR_TOO_LARGE;
   }
   bk.nseg = nseg;

@@ -50,6 +50,8 @@ def roofline_ms(comp: Compressor, n: int, N: int, topo: str, peaks) -> dict:
         if topo == "ps" and ef:
             hbm += 8.0 * n / N                        # server residual of the owned chunk
     pay = comp.payload_bytes(chunk_elems(n, N))
+    if not sp.sparse:
+        pay *= 2          # the fused dense kernels ship codes in {data, epoch} slots
     link = pay * (N - 1) * (1 if topo == "ring" else 2)   # bytes this rank stores into peers
     t_hbm = hbm / (peaks["hbm_gbs"] * 1e9) * 1e3
     t_link = link / (NVLINK_GBS_PER_DIR * 1e9) * 1e3
