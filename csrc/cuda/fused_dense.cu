@@ -106,6 +106,9 @@ __device__ __forceinline__ uint32_t ll_finish(const uint2* slot, uint2 v, const 
   while (true) {
     v = ll_load(slot);
     if (v.y == cm.epoch) break;
+    // back off: thousands of threads polling L2 would slow the GEMMs of backward
+    // that run next to this kernel while a peer is late
+    if (polls > 4) __nanosleep(polls > 64 ? 400 : 100);
     if ((++polls & 63u) == 0 && (*poisoned || global_timer_ns() - t0 > cm.timeout_ns)) {
       atomicCAS(status, 0u, code);
       *poisoned = 1;
