@@ -92,7 +92,11 @@ def cpu():
 
 
 # symbols added by later translation units of the CPU library (planner, scheduler)
-_CPU_OPTIONAL: dict = {}
+_CPU_OPTIONAL: dict = {
+    "hp_plan_buckets": (C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64,
+                        C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                        C.c_void_p, C.c_void_p, C.c_void_p),
+}
 
 
 def cuda():

@@ -126,6 +126,18 @@ class Emitter:
                     self.order.append(name)
             self.maps.append((name, v))
             self.stages.append(("map", len(self.maps) - 1))
+        elif isinstance(v, F.Call) and v.fn in ("topk", "scatter"):
+            # library-lowered stages: exact top-k selection / sparse scatter of the
+            # run-time library (radix select in shared memory, block compaction)
+            if tgt.kind != "param_vector":
+                raise CompileError(f"{v.fn} needs a vector parameter on the left", st.line)
+            if v.fn == "topk":
+                if len(v.args) not in (2, 3) or not all(isinstance(x, F.Name) for x in
+                                                          (v.args[0],) + tuple(v.args[2:])):
+                    raise CompileError("topk(vector, k[, companion]) takes vector names", st.line)
+            elif len(v.args) != 2 or not isinstance(v.args[0], F.Name):
+                raise CompileError("scatter(payload, scale) takes a payload vector and a scale", st.line)
+            self.stages.append((v.fn, name, v))
         elif isinstance(v, F.Concat):
             if tgt.kind != "param_vector":
                 raise CompileError("the left-hand side of concat must be a function parameter", st.line)
@@ -344,6 +356,24 @@ class Emitter:
                     rows.append(f"  c.n_{s.name} = (uint64_t)({self.expr(s.count, set())});")
         return "\n".join(rows)
 
+    def _depends_on_extracted(self, e) -> bool:
+        if isinstance(e, F.Name):
+            sy = self.syms.get(e.id)
+            if sy is None:
+                return False
+            if sy.kind == "extracted":
+                return True
+            return sy.kind == "derived" and self._depends_on_extracted(sy.expr)
+        if not isinstance(e, F.Expr):
+            return False
+        for f in getattr(e, "__dataclass_fields__", {}):
+            v = getattr(e, f)
+            if isinstance(v, F.Expr) and self._depends_on_extracted(v):
+                return True
+            if isinstance(v, list) and any(isinstance(a, F.Expr) and self._depends_on_extracted(a) for a in v):
+                return True
+        return False
+
     def _depends_on_reduced(self, e) -> bool:
         if isinstance(e, F.Name):
             s = self.syms.get(e.id)
@@ -525,7 +555,46 @@ namespace compll_gen_{name} {{
             if ty.vector:
                 n_main = n_main or f"n_{pname}"
         rows = []
+        uses_lib = any(st[0] in ("topk", "scatter") for st in self.stages)
+        if uses_lib:
+            rows.append("  compll_gen_%s::Ctx h;  // host copy of the parameters for library calls" % name)
+            for ty, pname in self.fn.params:
+                rows.append(f"  h.v_{pname} = p_{pname};")
+                if ty.vector:
+                    rows.append(f"  h.n_{pname} = n_{pname};")
+            for sname in self.order:
+                sy = self.syms[sname]
+                if sy.kind == "derived" and not self._depends_on_reduced(sy.expr) and \
+                        not self._depends_on_extracted(sy.expr):
+                    rows.append(f"  h.v_{sname} = ({C_TYPES[sy.type.name]})({self.expr(sy.expr, set(), 'h.')});")
         for gi, st in enumerate(self.stages):
+            if st[0] == "topk":
+                _, target, call = st
+                vec = call.args[0].id
+                comp = call.args[2].id if len(call.args) == 3 else None
+                kexp = self.expr(call.args[1], set(), "h.")
+                rows.append(f"""  {{
+    const uint64_t k = (uint64_t)({kexp});
+    if (k < 1 || k > n_{vec}) return -1;
+    if (n_{target} < hp_sparse_payload_bytes(k)) return -2;
+    int rc = hp_cuda_sparse_encode({4 if comp else 5}, nullptr, p_{vec}, {('p_' + comp) if comp else 'nullptr'}, n_{vec}, k, k, 0.0f, 0,
+                                   reinterpret_cast<uint8_t*>(p_{target}),
+                                   reinterpret_cast<uint8_t*>(scratch) + (kScalarBytes / 256 * 256 + 256), kLibScratch, 0, stream);
+    if (rc) return rc;
+  }}""")
+                continue
+            if st[0] == "scatter":
+                _, target, call = st
+                src = call.args[0].id
+                sexp = self.expr(call.args[1], set(), "h.")
+                rows.append(f"""  {{
+    if (n_{src} < 16) return -1;
+    const uint64_t kmax = (n_{src} - 16) / 8;   // capacity of the payload buffer in pairs
+    int rc = hp_cuda_sparse_decode(reinterpret_cast<const uint8_t*>(p_{src}), p_{target}, n_{target},
+                                   kmax, (float)({sexp}), 0, stream);
+    if (rc) return rc;
+  }}""")
+                continue
             if st[0] == "reduce":
                 rows.append(f"  compll_gen_{name}::{name}_reduce{gi}_kernel<<<grid, 256, 0, st>>>"
                             f"({self.kernel_args()}, partials, ticket);")
@@ -537,17 +606,30 @@ namespace compll_gen_{name} {{
   (void)partials; (void)ticket;
 """
         launches = "\n".join(rows)
+        lib_decl = ""
+        if uses_lib:
+            lib_decl = """
+// run-time library entry points (libhipress_cuda.so)
+extern "C" int hp_cuda_sparse_encode(int alg, const float* g, float* a, float* u, uint64_t n, uint64_t k,
+                                     uint64_t kmax, float momentum, int update, uint8_t* out,
+                                     void* workspace, uint64_t workspace_bytes, int max_ctas, void* stream);
+extern "C" int hp_cuda_sparse_decode(const uint8_t* payload, float* out, uint64_t n, uint64_t kmax,
+                                     float scale, int accumulate, void* stream);
+static inline uint64_t hp_sparse_payload_bytes(uint64_t k) { return 16 + 2 * ((4 * k + 15) / 16 * 16); }
+"""
         return f"""// Generated by hipress_b200.compll: launcher of {name}.
 #include "{name}_body.cuh"
-
+{lib_decl}
 namespace {{
 constexpr int kMaxBlocks = 1184;  // 148 SMs x 8
+constexpr uint64_t kScalarBytes = (16 + {max(nred, 1)} * kMaxBlocks + 4) * sizeof(float) + 240;
+constexpr uint64_t kLibScratch = {'(49216 + (8ull << 20))' if uses_lib else '0'};  // radix histograms + candidate list
 }}
 
 extern "C" {{
 
 // bytes of device scratch the launcher needs (zero-initialised once by the caller)
-uint64_t compll_{name}_scratch_bytes() {{ return (16 + {max(nred, 1)} * kMaxBlocks + 4) * sizeof(float); }}
+uint64_t compll_{name}_scratch_bytes() {{ return kScalarBytes / 256 * 256 + 256 + kLibScratch; }}
 
 int compll_{name}({sig}) {{
   cudaStream_t st = (cudaStream_t)stream;
@@ -562,6 +644,10 @@ int compll_{name}({sig}) {{
 
 }}  // extern "C"
 """
+
+    @property
+    def uses_library(self) -> bool:
+        return any(st[0] in ("topk", "scatter") for st in self.stages)
 
     def register_source(self, framework: str = "torch") -> str:
         """Python registration (``-r -f torch``): binds the launcher to torch tensors."""

@@ -30,14 +30,17 @@ def generate_files(path, outdir="output", *, body=True, wrapper=True, register=T
         (d / f"{name}.py").write_text(em.register_source(framework))
         written.append(d / f"{name}.py")
     if build:
-        written.append(compile_generated(d, name))
+        written.append(compile_generated(d, name, uses_library=em.uses_library))
     return written
 
 
-def compile_generated(d: Path, name: str, nvcc: str = "nvcc") -> Path:
+def compile_generated(d: Path, name: str, nvcc: str = "nvcc", uses_library: bool = False) -> Path:
     out = d / f"lib{name}.so"
     cmd = [nvcc, *NVCC_FLAGS, "-shared", "-I", str(INCLUDE), "-I", str(d), "-o", str(out),
            str(d / f"{name}_wrapper.cu")]
+    if uses_library:  # top-k / scatter stages call into the run-time library
+        libdir = ROOT / "hipress_b200" / "_native"
+        cmd += ["-L", str(libdir), "-lhipress_cuda", "-Xlinker", f"-rpath={libdir}"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed on generated code:\n" + r.stderr[-4000:])

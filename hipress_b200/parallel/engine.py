@@ -180,48 +180,36 @@ class GradSyncEngine:
                 raise RuntimeError(f"rank {self.R} and rank {q} disagree on the gradient list or plan")
 
     def _make_buckets(self):
-        cfg = self.cfg
-        buckets, cur_f, cur_p = [], None, None
-        bytes_f = bytes_p = 0
-
-        def close(which):
-            nonlocal cur_f, cur_p, bytes_f, bytes_p
-            if which == "f" and cur_f is not None:
-                buckets.append(cur_f)
-                cur_f, bytes_f = None, 0
-            if which == "p" and cur_p is not None:
-                buckets.append(cur_p)
-                cur_p, bytes_p = None, 0
-
-        # gradients become ready roughly in reverse registration order
-        for e in reversed(self.entries):
-            if e.compress and self.backend != "allreduce":
-                parts = split_partitions(e.numel, e.partitions)
-                if cur_f is not None and (len(cur_f.segs) + len(parts) > MAX_SEGS
-                                          or bytes_f + 4 * e.numel > cfg.bucket_bytes):
-                    close("f")
-                if cur_f is None:
-                    cur_f = Bucket(0, True)
-                while len(parts) > MAX_SEGS:  # a tensor alone in its bucket: fewer, larger parts
-                    parts = split_partitions(e.numel, len(parts) // 2)
-                cur_f.entries.append(e)
-                cur_f.segs += [Segment(e, lo, hi, i) for i, (lo, hi) in enumerate(parts)]
-                bytes_f += 4 * e.numel
-            else:
-                if cur_p is not None and bytes_p + 4 * e.numel > cfg.plain_bucket_bytes:
-                    close("p")
-                if cur_p is None:
-                    cur_p = Bucket(0, False)
-                cur_p.entries.append(e)
-                bytes_p += 4 * e.numel
-        # order buckets by when they complete: backward produces gradients in
-        # descending registration order, so a bucket is complete once its
-        # lowest-index entry is; launch order must follow completion order
-        rest = [b for b in (cur_f, cur_p) if b is not None]
-        allb = sorted(buckets + rest, key=lambda b: -min(x.index for x in b.entries))
-        for i, b in enumerate(allb):
-            b.index = i
-        return allb
+        """Bucket planning is done by the native planner (csrc/cpu/planner.cpp):
+        fused buckets of tile-aligned segments for compressed gradients, plain
+        buckets for the rest, in completion (= launch) order."""
+        import numpy as np
+        from .._native import lib as _lib
+        cfg, n = self.cfg, len(self.entries)
+        fused_ok = self.backend != "allreduce"
+        numel = np.array([e.numel for e in self.entries], dtype=np.uint64)
+        comp = np.array([1 if (e.compress and fused_ok) else 0 for e in self.entries], dtype=np.int32)
+        parts = np.array([e.partitions for e in self.entries], dtype=np.int32)
+        cap = int(sum(max(1, int(p)) for p in parts)) + n + MAX_SEGS
+        bucket_of = np.zeros(n, dtype=np.int32)
+        bucket_fused = np.zeros(n, dtype=np.int32)
+        sb, se, sp = (np.zeros(cap, dtype=np.int32) for _ in range(3))
+        slo, shi = np.zeros(cap, dtype=np.uint64), np.zeros(cap, dtype=np.uint64)
+        nseg = np.zeros(1, dtype=np.int32)
+        nb = _lib.cpu().hp_plan_buckets(
+            n, numel.ctypes.data, comp.ctypes.data, parts.ctypes.data, cfg.bucket_bytes,
+            cfg.plain_bucket_bytes, bucket_of.ctypes.data, bucket_fused.ctypes.data, cap,
+            sb.ctypes.data, se.ctypes.data, sp.ctypes.data, slo.ctypes.data, shi.ctypes.data,
+            nseg.ctypes.data)
+        if nb < 0:
+            _lib.check(nb, "bucket planner")
+        buckets = [Bucket(i, bool(bucket_fused[i])) for i in range(nb)]
+        for i in reversed(range(n)):  # entries of a bucket in the order backward produces them
+            buckets[int(bucket_of[i])].entries.append(self.entries[i])
+        for j in range(int(nseg[0])):
+            buckets[int(sb[j])].segs.append(
+                Segment(self.entries[int(se[j])], int(slo[j]), int(shi[j]), int(sp[j])))
+        return buckets
 
     def _alloc_state(self):
         if not self.compress:

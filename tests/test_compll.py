@@ -180,3 +180,73 @@ def test_reference_dsl_sources_run(tmp_path):
     gap = (g.max() - g.min()).item() / 3
     inside = g < g.max() - gap  # the source does not clamp a round-up at the maximum
     assert (out - g)[inside].abs().max().item() <= gap * 1.001
+
+
+def test_topk_and_scatter_lower_to_library_stages():
+    em = generate((PSE / "DgcEncode.pse").read_text())
+    assert [s[0] for s in em.stages] == ["map", "map", "topk"] and em.uses_library
+    w = em.wrapper_source()
+    assert "hp_cuda_sparse_encode(4, nullptr, p_accum_v, p_momentum_u" in w
+    em = generate((PSE / "GradDropDecode.pse").read_text())
+    assert [s[0] for s in em.stages] == ["scatter"]
+    with pytest.raises(CompileError):
+        generate("void f(float* g, uint8* c){ float x = 1.0; x = topk(g, 3); }")
+
+
+@pytest.mark.gpu
+def test_generated_decode_accumulate(tmp_path):
+    enc, acc = _load(tmp_path, "TbqEncode"), _load(tmp_path, "TbqDecodeAccumulate")
+    n = 30001
+    torch.manual_seed(4)
+    g = torch.randn(n, device="cuda") * 0.02
+    r = torch.zeros(n, device="cuda")
+    comp = torch.zeros(4 + (n + 3) // 4, dtype=torch.uint8, device="cuda")
+    enc(g, r, comp, 0.01)
+    base = torch.randn(n, device="cuda")
+    out = base.clone()
+    acc(comp, out, 0.25)
+    want = base + 0.25 * torch.where(g >= 0.01, 0.01, torch.where(g <= -0.01, -0.01, 0.0))
+    assert torch.allclose(out, want.float(), atol=1e-7)
+
+
+@pytest.mark.gpu
+def test_generated_graddrop_and_dgc_use_the_library_topk(tmp_path):
+    import math
+    n, ratio = 200003, 0.001
+    k = max(int(math.ceil(torch.tensor(ratio, dtype=torch.float32).item() * n)), 1)
+    nbytes = 16 + 2 * ((4 * k + 15) // 16 * 16)
+    torch.manual_seed(9)
+    g = torch.randn(n, device="cuda")
+    # GradDrop
+    enc, dec = _load(tmp_path, "GradDropEncode"), _load(tmp_path, "GradDropDecode")
+    r0 = torch.randn(n, device="cuda") * 0.3
+    r = r0.clone()
+    comp = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    enc(g, r, comp, ratio)
+    out = torch.ones(n, device="cuda")
+    dec(comp, out, 0.5)
+    torch.cuda.synchronize()
+    x = g + r0
+    top = torch.topk(x.abs(), k).indices
+    assert int((out != 0).sum()) == k
+    assert torch.allclose(out[top], 0.5 * x[top])
+    assert torch.all(r[top] == 0)
+    mask = torch.ones(n, dtype=torch.bool, device="cuda")
+    mask[top] = False
+    assert torch.allclose(r[mask], x[mask])
+    # DGC
+    enc = _load(tmp_path, "DgcEncode")
+    u = torch.randn(n, device="cuda") * 0.1
+    v = torch.randn(n, device="cuda") * 0.1
+    u_ref = 0.9 * u + g
+    v_ref = v + u_ref
+    comp.zero_()
+    enc(g, u, v, comp, ratio, 0.9)
+    dec(comp, out, 1.0)
+    torch.cuda.synchronize()
+    top = torch.topk(v_ref.abs(), k).indices
+    assert torch.allclose(out[top], v_ref[top], rtol=1e-6)
+    assert torch.all(v[top] == 0) and torch.all(u[top] == 0)
+    mask = torch.ones(n, dtype=torch.bool, device="cuda")
+    mask[top] = False
+    assert torch.allclose(v[mask], v_ref[mask], rtol=1e-6) and torch.allclose(u[mask], u_ref[mask], rtol=1e-6)
