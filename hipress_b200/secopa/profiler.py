@@ -102,8 +102,34 @@ def profile(algorithm="tbq", nnodes=8, min_elems=1 << 14, max_elems=1 << 26, ite
                        source=f"measured on {torch.cuda.get_device_name()} ({'real' if real else 'emulated'} ranks)")
 
 
+def profile_from_sweep(path, algorithm="tbq") -> CostProfile:
+    """Fit a profile from the rows a multi-GPU run of
+    ``hipress_b200.bench.sweep_multi`` wrote (fused ring / PS and NCCL all-reduce
+    times per size, measured on real ranks)."""
+    rows = [r for r in json.load(open(path)) if r["alg"] == algorithm]
+    if not rows:
+        raise ValueError(f"no rows for {algorithm} in {path}")
+    n = rows[0]["n_gpus"]
+
+    def fit(key, topo=None):
+        pts = [(r["bytes"] / 4.0, r[key]) for r in rows
+               if key in r and r[key] and (topo is None or r["topo"] == topo)]
+        pts = sorted(set(pts))
+        return fit_linear([p[0] for p in pts], [p[1] for p in pts]) if pts else None
+
+    send = LinearCost(4.0 / 770e9 * 1e3, 0.003, 0.003)
+    enc = LinearCost(1.65e-9, 0.0208, 0.0196)   # stand-alone kernels, one B200 (profile())
+    dec = LinearCost(1.26e-9, 0.0178, 0.0183)
+    return CostProfile(nodes=n, encode=enc, decode=dec, ring_send=send, gather=send, broadcast=send,
+                       comp_ratio=1.0 / 16, fused_ring=fit("fused_ms", "ring"),
+                       fused_ps=fit("fused_ms", "ps"), allreduce=fit("allreduce_ms"),
+                       source=f"fitted from {n}-GPU sweep rows ({algorithm})")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description="measure B200 cost coefficients for SeCoPa")
+    ap.add_argument("--from-sweep", default=None,
+                    help="fit from a sweep_multi JSON instead of measuring now")
     ap.add_argument("--algorithm", default="tbq")
     ap.add_argument("--nnodes", type=int, default=8)
     ap.add_argument("--min-elems", type=int, default=1 << 14)
@@ -112,6 +138,12 @@ def main(argv=None):
     ap.add_argument("--output", default="secopa_profile.json")
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args(argv)
+    if a.from_sweep:
+        prof = profile_from_sweep(a.from_sweep, a.algorithm)
+        with open(a.output, "w") as f:
+            f.write(prof.to_json())
+        print(a.output)
+        return
     from ..parallel import comm
     comm.init()
     prof = profile(a.algorithm, a.nnodes, a.min_elems, a.max_elems, a.iters, verbose=a.verbose)

@@ -45,3 +45,38 @@ def test_partitions_are_tile_aligned_and_capped():
 def test_uncompressed_run_has_only_plain_buckets():
     eng = _engine([5000, 10], algorithm="none")
     assert all(not b.fused for b in eng.buckets) and eng.backend == "allreduce"
+
+
+def test_measured_profile_compresses_only_what_pays_off_on_nvswitch():
+    """With coefficients fitted on the 8 x B200 box the planner keeps small
+    gradients on the plain all-reduce and compresses the large FC layers."""
+    from pathlib import Path
+    from hipress_b200.secopa import CostProfile, Planner, read_gradient_list
+    root = Path(__file__).resolve().parents[1]
+    prof = CostProfile.from_json((root / "hipress_b200/secopa/profiles/b200_tbq_n8.json").read_text())
+    assert prof.nodes == 8 and prof.fused_ring is not None and prof.allreduce is not None
+    rows = Planner(prof).plan(read_gradient_list(root / "tests/data/vgg19_gradients.txt"), "RING")
+    by = {r[0]: r for r in rows}
+    assert by["vgg0_dense0_weight"][2] == "y" and by["vgg0_dense1_weight"][2] == "y"
+    assert by["vgg0_conv0_weight"][2] == "n" and by["vgg0_dense2_bias"][2] == "n"
+
+
+def test_gradient_accumulation_and_unused_parameters():
+    used = torch.nn.Parameter(torch.zeros(5000))
+    unused = torch.nn.Parameter(torch.zeros(3000))
+    small = torch.nn.Parameter(torch.zeros(10))
+    params = [("used", used), ("unused", unused), ("small", small)]
+    opt = hp.DistributedOptimizer(torch.optim.SGD([p for _, p in params], lr=1.0), params,
+                                  algorithm="tbq", comp_threshold=1000, threshold=0.01,
+                                  backward_passes_per_step=2)
+    for micro in range(2):                  # two micro-batches, one synchronisation
+        (used.sum() * 0.02 + small.sum()).backward()
+        if micro == 0:
+            assert not any(b.launched for b in opt.engine.buckets)
+    opt.step()
+    # accumulated gradient 0.04 per element -> one +threshold level sent, rest kept
+    assert torch.allclose(used.detach(), torch.full((5000,), -0.01))
+    assert torch.allclose(small.detach(), torch.full((10,), -2.0))
+    assert torch.all(unused.detach() == 0) and unused.grad is not None
+    res = opt.engine.entries[0].state["residual"]
+    assert torch.allclose(res, torch.full((5000,), 0.03))
