@@ -3,7 +3,7 @@ the fused ring / PS kernels with N emulated ranks, fp32 gradients of 4 KB - 1 GB
 (powers of 4), values N(0,1) seed 0.  Reports milliseconds, achieved GB/s over the
 algorithmic HBM bytes and the fraction of the measured copy bandwidth.
 
-    python -m hipress_b200.bench.sweep --what ops --out gpurun_out/sweep_ops.json
+    python -m hipress_b200.bench.sweep --what ops --out sweep_ops.json
     python -m hipress_b200.bench.sweep --what fused --ranks 8 --max-mb 256
 """
 from __future__ import annotations

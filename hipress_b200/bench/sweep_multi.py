@@ -106,7 +106,7 @@ def main(argv=None):
                 elif topo == "ps":
                     fused = FusedSparseBucket(comp.spec, [n], N, R)
                 if fused is not None:
-                    arena = SymmetricArena(fused.region_bytes() + 4096)
+                    arena = SymmetricArena(fused.region_bytes() + 8192)
                     if comp.spec.sparse:
                         fused.bind(arena.carve(fused.region_bytes()), status, dev)
                         acc = st["accum_v"] if "accum_v" in st else st["residual"]

@@ -250,7 +250,7 @@ class GradSyncEngine:
                 impls.append(FusedDenseBucket(
                     self.comp.spec, cfg.topology, [s.n for s in b.segs], self.N, self.R,
                     ctas=cfg.partition_ctas if on_part else cfg.ctas, timeout_s=cfg.timeout_s))
-            total = sum(i.region_bytes() for i in impls) + 4096
+            total = sum(i.region_bytes() + 512 for i in impls) + 4096
             self.arena = SymmetricArena(total, self.group)
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
             for b, impl in zip(fused_buckets, impls):
@@ -458,9 +458,11 @@ class GradSyncEngine:
         self._status_event.record(self.comm_stream)
 
     def check(self):
-        """Blocking check of the device status words."""
+        """Blocking check of the device status words and of the guard words
+        behind every bucket's region of the symmetric arena."""
         if self.arena is None:
             return
+        self.arena.check_guards()
         from .fused import HipressTimeoutError, decode_status
         torch.cuda.synchronize()
         words = [w & 0xFFFFFFFF for w in self.status.cpu().tolist()]

@@ -123,7 +123,7 @@ def setup_engine_buckets(engine, fused_buckets) -> bool:
     from .symm import SymmetricArena
     impls = [FusedSparseBucket(engine.comp.spec, [s.n for s in b.segs], engine.N, engine.R,
                                ctas=0, timeout_s=cfg.timeout_s) for b in fused_buckets]
-    total = sum(i.region_bytes() for i in impls) + 4096
+    total = sum(i.region_bytes() + 512 for i in impls) + 4096
     engine.arena = SymmetricArena(total, engine.group)
     engine.status = torch.zeros(4, dtype=torch.int32, device=engine.device)
     for b, impl in zip(fused_buckets, impls):

@@ -44,14 +44,45 @@ class SymmetricArena:
                 self._opened.append(pp.value)
             dist.barrier(group=group)
         self._cursor = 0
+        self._guards = []
+
+    GUARD_BYTES = 256
+    GUARD_WORD = 0x5AFEC0DE
 
     def carve(self, nbytes: int):
-        """Reserve `nbytes` at the same offset on every rank; returns per-rank addresses."""
+        """Reserve `nbytes` at the same offset on every rank; returns per-rank
+        addresses.  Every region is followed by a guard block of canary words in
+        this rank's arena; :meth:`check_guards` reports a region that was overrun
+        (by a local kernel or by a peer's stores)."""
         off = self._cursor
-        self._cursor += (int(nbytes) + 255) // 256 * 256
+        size = (int(nbytes) + 255) // 256 * 256
+        self._cursor += size + self.GUARD_BYTES
         if self._cursor > self.nbytes:
             raise MemoryError("symmetric arena exhausted")
+        self._guards.append(off + size)
+        g = self._view(off + size, self.GUARD_BYTES // 4)
+        g.fill_(self.GUARD_WORD)
         return [p + off for p in self.ptrs]
+
+    def _view(self, offset: int, words: int) -> torch.Tensor:
+        """int32 tensor over a piece of the local arena (no copy)."""
+        class _Arr:  # minimal __cuda_array_interface__ carrier
+            pass
+        a = _Arr()
+        a.__cuda_array_interface__ = {"shape": (words,), "typestr": "<i4",
+                                      "data": (self.local + offset, False), "version": 3}
+        return torch.as_tensor(a, device=torch.device("cuda", torch.cuda.current_device()))
+
+    def check_guards(self):
+        """Raises if any guard block behind a carved region was overwritten."""
+        torch.cuda.synchronize()
+        bad = []
+        for i, off in enumerate(self._guards):
+            g = self._view(off, self.GUARD_BYTES // 4)
+            if not bool((g == self.GUARD_WORD).all()):
+                bad.append(i)
+        if bad:
+            raise RuntimeError(f"symmetric arena: regions {bad} were overrun (guard words changed)")
 
     def close(self):
         L = _lib.cuda()

@@ -158,3 +158,20 @@ def test_bounded_wait_reports_and_returns():
     assert status[0].item() == 0
     # the context is still usable
     assert torch.ones(8, device="cuda").sum().item() == 8
+
+
+def test_arena_guard_words_detect_an_overrun():
+    from hipress_b200.parallel.symm import SymmetricArena
+    import hipress_b200 as hp
+    hp.init()
+    arena = SymmetricArena(1 << 16)
+    a = arena.carve(1000)[0]
+    b = arena.carve(512)[0]
+    assert b - a == 1024 + SymmetricArena.GUARD_BYTES
+    arena.check_guards()
+    # a writer that runs past its region (here: 8 bytes into the guard of region 0)
+    over = arena._view(1024, 2)
+    over.fill_(7)
+    with pytest.raises(RuntimeError, match="regions \\[0\\]"):
+        arena.check_guards()
+    arena.close()
