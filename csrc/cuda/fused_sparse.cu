@@ -243,6 +243,128 @@ sp_pull_kernel(const SpBucket bk, const HpComm cm, int R, int E) {
                blockIdx.x, gridDim.x);
 }
 
+// ---------------------------------------------------------------- ring
+// One hop of the sparse ring for every tensor of the bucket (unit y = seg).  At hop
+// h rank R works on chunk (R - h) mod N: the predecessor's pairs are added into the
+// local accumulator, then the state update, the exact top-k selection and the
+// compaction run, and the pairs go into the successor's inbox -- or, at the last
+// hop, into every rank's inbox.
+// STAGE 0: wait + add incoming   1: update + hist0   2: split   3,4: candidate digit
+//       passes   5: candidate compaction + flag(s)   6,7,8: overflow path
+template <int STAGE>
+__global__ void __launch_bounds__(kSpThreads)
+sp_ring_kernel(const SpBucket bk, const HpComm cm, int R, int E, int hop, uint32_t* ws_all,
+               uint8_t* cand_all) {
+  __shared__ uint32_t sh[kBins];
+  __shared__ FindSmem fs;
+  __shared__ EmitSmem es;
+  __shared__ WaitState wst;
+  const int N = cm.nranks;
+  const int si = blockIdx.y;
+  const int c = (R - hop + N) % N;
+  const bool last_hop = hop == N - 1;
+  const SpSeg& sg = bk.seg[si];
+  const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, c);
+  uint32_t* ws = ws_all + ((size_t)hop * bk.nseg + si) * kWsWords;
+  float* cand_val = reinterpret_cast<float*>(cand_all + (sg.cand_push + (uint64_t)c * sg.cap) * 8);
+  uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + sg.cap);
+  const size_t off = (size_t)c * sg.chunk;
+  const float* g = sg.g + E * cm.emu_stride_g + off;
+  float* a = sg.a + E * cm.emu_stride_r + off;
+  float* u = sg.u ? sg.u + E * cm.emu_stride_r + off : nullptr;
+  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
+  const uint32_t k = (uint32_t)sparse_k(len, bk.ratio);
+  EmitDst d;
+  if (!last_hop) {
+    d.n = 1;
+    d.out[0] = reinterpret_cast<uint8_t*>(cm.inbox[(R + 1) % N]) + (size_t)hop * bk.slot_bytes + sg.pay_off;
+  } else {
+    d.n = N;
+    for (int q = 0; q < N; ++q)
+      d.out[q] = reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) +
+                 (size_t)(N - 1 + R) * bk.slot_bytes + sg.pay_off;
+  }
+  bool last = false;
+  if (STAGE == 0) {
+    if (hop == 0) return;
+    wait_init(wst);
+    wait_flag(reinterpret_cast<const uint32_t*>(cm.flags[R]) + (size_t)(hop - 1) * bk.nseg + si,
+              cm.epoch, cm.timeout_ns, status,
+              HP_STATUS_TIMEOUT | (6u << 16) | ((uint32_t)(hop - 1) << 8) | (si & 255), wst);
+    if (len == 0) return;
+    scatter_body(reinterpret_cast<const uint8_t*>(cm.inbox[R]) + (size_t)(hop - 1) * bk.slot_bytes +
+                     sg.pay_off,
+                 a, len, sg.kmax, 1.0f, 1, blockIdx.x, gridDim.x);
+    return;
+  } else if (STAGE == 1) {
+    if (len == 0) return;
+    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
+    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
+    return;
+  } else if (STAGE == 2) {
+    if (len == 0) return;
+    __shared__ SplitSmem sp;
+    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, sp, blockIdx.x, gridDim.x);
+    return;
+  } else if (STAGE == 3 || STAGE == 4) {
+    if (len == 0 || ws[kWsOverflow]) return;
+    if (STAGE == 3) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    return;
+  } else if (STAGE == 5) {
+    if (len == 0) {
+      last = blockIdx.x == 0 && threadIdx.x == 0;
+      if (last)
+        for (int q = 0; q < d.n; ++q) write_empty_header(d.out[q], bk.alg);
+    } else {
+      if (ws[kWsOverflow]) return;
+      last = emit_body(bk.alg, cand_val, u, ws[kWsCandCount], k, sg.kmax, d, ws, fs, es, blockIdx.x,
+                       gridDim.x, cand_idx, a, len);
+    }
+  } else if (STAGE == 6 || STAGE == 7) {
+    if (len == 0 || !ws[kWsOverflow]) return;
+    if (STAGE == 6) pass_body<1>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    else pass_body<2>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    return;
+  } else {
+    if (len == 0 || !ws[kWsOverflow]) return;
+    last = emit_body(bk.alg, a, u, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+  }
+  if (last) {
+    __threadfence_system();
+    if (!last_hop) {
+      st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + 1) % N]) + (size_t)hop * bk.nseg + si,
+                     cm.epoch);
+    } else {
+      for (int q = 0; q < N; ++q)
+        st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + q) % N]) +
+                           (size_t)(N - 1 + R) * bk.nseg + si,
+                       cm.epoch);
+    }
+  }
+}
+
+// gather of the ring: unit y = seg * N + src; rank src finalised chunk src + 1
+__global__ void __launch_bounds__(kSpThreads)
+sp_ring_gather_kernel(const SpBucket bk, const HpComm cm, int R, int E) {
+  __shared__ WaitState wst;
+  const int N = cm.nranks;
+  const int si = blockIdx.y / N, src = blockIdx.y % N;
+  const int c = (src + 1) % N;
+  const SpSeg& sg = bk.seg[si];
+  const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, c);
+  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
+  wait_init(wst);
+  wait_flag(reinterpret_cast<const uint32_t*>(cm.flags[R]) + (size_t)(N - 1 + src) * bk.nseg + si,
+            cm.epoch, cm.timeout_ns, status,
+            HP_STATUS_TIMEOUT | (7u << 16) | ((uint32_t)src << 8) | (si & 255), wst);
+  if (len == 0) return;
+  const uint8_t* p = reinterpret_cast<const uint8_t*>(cm.inbox[R]) +
+                     (size_t)(N - 1 + src) * bk.slot_bytes + sg.pay_off;
+  scatter_body(p, sg.out + E * cm.emu_stride_out + (size_t)c * sg.chunk, len, sg.kmax, bk.inv_n, 0,
+               blockIdx.x, gridDim.x);
+}
+
 static int build_sp_bucket(int alg, float ratio, float momentum, const HpSeg* segs,
                            void* const* accs, void* const* us, int nseg, int nranks, SpBucket& bk) {
   if (nseg < 1 || nseg > HP_MAX_SEGS || nranks < 1 || nranks > HP_MAX_RANKS) return HP_ERR_BAD_ARG;
@@ -369,6 +491,60 @@ int hp_cuda_fused_sparse_ps(int alg, float ratio, float momentum, const HpSeg* s
     const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
     sp_pull_kernel<0><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E);
     sp_pull_kernel<1><<<gpull, kSpThreads, 0, st>>>(bk, *comm, R, E);
+  }
+  return (int)cudaGetLastError();
+}
+
+// One synchronisation of a bucket through the ring topology: N hops, each a fixed
+// sequence of launches over all tensors of the bucket, then the gather.  Same
+// arguments as hp_cuda_fused_sparse_ps (segs[i].sr is not used).
+int hp_cuda_fused_sparse_ring(int alg, float ratio, float momentum, const HpSeg* segs,
+                              void* const* us, int nseg, const HpComm* comm, void* ws, int ctas,
+                              void* stream) {
+  if (!comm || ctas > 1024) return HP_ERR_BAD_ARG;
+  SpBucket bk;
+  const int N = comm->nranks;
+  int rc = build_sp_bucket(alg, ratio, momentum, segs, nullptr, us, nseg, N, bk);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int ranks_here = comm->emulate ? N : 1;
+  const size_t hist_words = (size_t)(nseg * N + nseg) * kWsWords;  // ring uses nseg * N of them
+  const size_t hist_bytes = align_up(hist_words * 4, 256);
+  const size_t ws_rank_bytes = hist_bytes + bk.cand_pairs * 8;
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  for (int r = 0; r < ranks_here; ++r) {
+    cudaError_t e = cudaMemsetAsync(wsb + (size_t)r * ws_rank_bytes, 0, hist_words * 4, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  auto per_unit = [&](int units) {
+    if (ctas > 0) return ctas;
+    int c = (148 * 4 + units - 1) / units;
+    return c < 4 ? 4 : (c > 592 ? 592 : c);
+  };
+  const dim3 gh(per_unit(nseg), nseg), ch(gh.x < 32 ? gh.x : 32, nseg);
+  const dim3 gpull(per_unit(nseg * N) < 16 ? per_unit(nseg * N) : 16, nseg * N);
+  // hop-major order: with emulated ranks the producer of a hop's input has
+  // always been issued before its consumer
+  for (int hop = 0; hop < N; ++hop) {
+    for (int r = 0; r < ranks_here; ++r) {
+      const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
+      uint32_t* w = reinterpret_cast<uint32_t*>(wsb + (size_t)r * ws_rank_bytes);
+      uint8_t* cd = wsb + (size_t)r * ws_rank_bytes + hist_bytes;
+      if (hop > 0) sp_ring_kernel<0><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<1><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<2><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<3><<<ch, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<4><<<ch, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<5><<<ch, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<6><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<7><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+      sp_ring_kernel<8><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
+    }
+  }
+  for (int r = 0; r < ranks_here; ++r) {
+    const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
+    sp_pull_kernel<0><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E);
+    sp_ring_gather_kernel<<<gpull, kSpThreads, 0, st>>>(bk, *comm, R, E);
   }
   return (int)cudaGetLastError();
 }

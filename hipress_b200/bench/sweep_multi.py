@@ -103,8 +103,8 @@ def main(argv=None):
                 fused = None
                 if not comp.spec.sparse:
                     fused = FusedDenseBucket(comp.spec, topo, [n], N, R, ctas=a.ctas)
-                elif topo == "ps":
-                    fused = FusedSparseBucket(comp.spec, [n], N, R)
+                else:
+                    fused = FusedSparseBucket(comp.spec, [n], N, R, topology=topo)
                 if fused is not None:
                     arena = SymmetricArena(fused.region_bytes() + 8192)
                     if comp.spec.sparse:

@@ -369,13 +369,13 @@ class GradSyncEngine:
                 a_ptrs.append(acc.data_ptr() + 4 * s.lo)
                 u = e.state.get("momentum_u")
                 u_ptrs.append(None if u is None else u.data_ptr() + 4 * s.lo)
-                sst = e.server_state[s.part]
+                sst = e.server_state[s.part] if e.server_state else {}
                 if sst.get("_scratch"):
                     sst["residual"].zero_()
-                sr_ptrs.append(sst["residual"].data_ptr())
+                sr_ptrs.append(sst["residual"].data_ptr() if "residual" in sst else None)
             b.impl.launch_ptrs(g_ptrs, a_ptrs, u_ptrs, g_ptrs, sr_ptrs,
                                stream=b.stream or self.comm_stream)
-            self.launch_count += 19
+            self.launch_count += 19 if self.cfg.topology == "ps" else 9 * self.N + 1
         elif b.impl is not None:
             g_ptrs, r_ptrs, sr_ptrs, ids = [], [], [], []
             rname = "residual"

@@ -24,18 +24,21 @@ def _bind():
                                              C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
                                              C.POINTER(C.c_uint64)]
         L.hp_cuda_fused_sparse_ps.restype = C.c_int
-        L.hp_cuda_fused_sparse_ps.argtypes = [C.c_int, C.c_float, C.c_float, C.POINTER(_lib.HpSeg),
-                                              C.POINTER(C.c_void_p), C.c_int, C.POINTER(_lib.HpComm),
-                                              C.c_void_p, C.c_int, C.c_void_p]
+        sig = [C.c_int, C.c_float, C.c_float, C.POINTER(_lib.HpSeg), C.POINTER(C.c_void_p), C.c_int,
+               C.POINTER(_lib.HpComm), C.c_void_p, C.c_int, C.c_void_p]
+        L.hp_cuda_fused_sparse_ps.argtypes = sig
+        L.hp_cuda_fused_sparse_ring.restype = C.c_int
+        L.hp_cuda_fused_sparse_ring.argtypes = sig
         _bound = True
     return L
 
 
 class FusedSparseBucket:
-    """One bucket (<= 40 tensors) of a top-k algorithm on the PS topology."""
+    """One bucket (<= 40 tensors) of a top-k algorithm on the PS or ring topology."""
 
     def __init__(self, spec: AlgSpec, sizes, nranks: int, rank: int, *, ctas: int = 0,
-                 emulate: bool = False, timeout_s: float = 2.0):
+                 emulate: bool = False, timeout_s: float = 2.0, topology: str = "ps"):
+        self.topology = topology.lower()
         if not spec.sparse:
             raise ValueError("FusedSparseBucket handles dgc / graddrop")
         self.spec, self.sizes = spec, [int(s) for s in sizes]
@@ -100,9 +103,9 @@ class FusedSparseBucket:
         cm.emu_stride_g, cm.emu_stride_r, cm.emu_stride_out, cm.emu_stride_sr = strides
         sp = self.spec
         us = self._us if sp.alg == DGC else None
-        rc = L.hp_cuda_fused_sparse_ps(sp.alg, sp.ratio, sp.momentum, self._segs, us, nseg,
-                                       C.byref(cm), self.ws.data_ptr(), self.ctas,
-                                       _lib.stream_ptr(stream))
+        fn = L.hp_cuda_fused_sparse_ps if self.topology == "ps" else L.hp_cuda_fused_sparse_ring
+        rc = fn(sp.alg, sp.ratio, sp.momentum, self._segs, us, nseg, C.byref(cm), self.ws.data_ptr(),
+                self.ctas, _lib.stream_ptr(stream))
         _lib.check(rc, "fused sparse launch")
 
     def check_status(self):
@@ -116,13 +119,14 @@ class FusedSparseBucket:
 
 def setup_engine_buckets(engine, fused_buckets) -> bool:
     """Called by GradSyncEngine for a sparse algorithm with the fused backend.
-    Returns False when the configuration has no fused kernels (ring topology)."""
+    Returns False when there is nothing to set up."""
     cfg = engine.cfg
-    if cfg.topology != "ps" or not fused_buckets:
+    if not fused_buckets:
         return False
     from .symm import SymmetricArena
     impls = [FusedSparseBucket(engine.comp.spec, [s.n for s in b.segs], engine.N, engine.R,
-                               ctas=0, timeout_s=cfg.timeout_s) for b in fused_buckets]
+                               ctas=0, timeout_s=cfg.timeout_s, topology=cfg.topology)
+             for b in fused_buckets]
     total = sum(i.region_bytes() + 512 for i in impls) + 4096
     engine.arena = SymmetricArena(total, engine.group)
     engine.status = torch.zeros(4, dtype=torch.int32, device=engine.device)
@@ -130,9 +134,9 @@ def setup_engine_buckets(engine, fused_buckets) -> bool:
         impl.bind(engine.arena.carve(impl.region_bytes()), engine.status, engine.device)
         b.impl = impl
         b.stream = engine.comm_stream
-        for s in b.segs:  # the owner always needs an accumulator for the summed payloads
+        for s in b.segs:  # PS: the owner always needs an accumulator for the summed payloads
             sst = s.entry.server_state[s.part]
-            if "residual" not in sst:
+            if cfg.topology == "ps" and "residual" not in sst:
                 sst["residual"] = torch.zeros(chunk_elems(s.n, engine.N), dtype=torch.float32,
                                               device=engine.device)
                 sst["_scratch"] = True

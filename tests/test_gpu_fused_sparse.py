@@ -5,7 +5,7 @@ import torch
 
 from hipress_b200.ops import Compressor
 from hipress_b200.parallel.fused_sparse import FusedSparseBucket
-from hipress_b200.parallel.simulate import chunk_elems, simulate_ps
+from hipress_b200.parallel.simulate import chunk_elems, simulate_ps, simulate_ring
 
 pytestmark = pytest.mark.gpu
 
@@ -54,6 +54,40 @@ def test_sparse_ps_emulated(name, N):
                 assert torch.allclose(SR[r, coffs[i]:coffs[i] + ch].cpu(), cpu_server[r][i]["residual"],
                                       rtol=1e-5, atol=1e-7)
         assert (O[0] != 0).sum().item() > 0
+
+
+@pytest.mark.parametrize("N", [1, 2, 3, 8])
+@pytest.mark.parametrize("name", ["dgc", "graddrop"])
+def test_sparse_ring_emulated(name, N):
+    torch.manual_seed(7 + N)
+    sizes = [150001, 8192, 300, 1 << 17]
+    c = Compressor(name, ratio=0.01)
+    b = FusedSparseBucket(c.spec, sizes, N, 0, ctas=8, emulate=True, topology="ring").bind_local("cuda")
+    total = sum(sizes)
+    offs = [sum(sizes[:i]) for i in range(len(sizes))]
+    G = torch.zeros(N, total, device="cuda")
+    A = torch.zeros(N, total, device="cuda")
+    U = torch.zeros(N, total, device="cuda") if name == "dgc" else None
+    O = torch.zeros(N, total, device="cuda")
+    cpu_states = [[c.new_state(s, "cpu") for s in sizes] for _ in range(N)]
+    acc_name = "accum_v" if name == "dgc" else "residual"
+    for step in range(3):
+        Gc = torch.randn(N, total)
+        G.copy_(Gc)
+        b.launch_ptrs([G[0, o:].data_ptr() for o in offs], [A[0, o:].data_ptr() for o in offs],
+                      [U[0, o:].data_ptr() for o in offs] if U is not None else None,
+                      [O[0, o:].data_ptr() for o in offs], [None] * len(sizes),
+                      strides=(total, total, total, 0))
+        torch.cuda.synchronize()
+        b.check_status()
+        for i, (o, s) in enumerate(zip(offs, sizes)):
+            gl = [Gc[r, o:o + s].contiguous() for r in range(N)]
+            ref = simulate_ring(c, gl, [cpu_states[r][i] for r in range(N)])
+            for r in range(N):
+                got = O[r, o:o + s].cpu()
+                assert torch.allclose(got, ref[r], rtol=1e-5, atol=1e-7), (name, N, step, i, r)
+                assert torch.equal(O[r, o:o + s], O[0, o:o + s])
+                assert torch.allclose(A[r, o:o + s].cpu(), cpu_states[r][i][acc_name], rtol=1e-5, atol=1e-7)
 
 
 def test_sparse_ps_through_the_optimizer_single_rank():

@@ -47,7 +47,8 @@ def _world():
 
 
 @pytest.mark.parametrize("alg,topo", [("tbq", "ring"), ("tbq", "ps"), ("onebit", "ring"),
-                                      ("terngrad", "ps"), ("dgc", "ps"), ("graddrop", "ps")])
+                                      ("terngrad", "ps"), ("dgc", "ps"), ("graddrop", "ps"),
+                                      ("dgc", "ring")])
 def test_fused_multigpu_matches_simulation(alg, topo):
     world, steps = _world(), 2
     res = spawn(_worker, world, alg, topo, steps, backend="nccl")
