@@ -170,6 +170,15 @@ def read_gradient_list(path) -> list[tuple[str, int]]:
     return rows
 
 
+def gradient_list_of(named_parameters) -> list[tuple[str, int]]:
+    """(name, element count) rows of a model, the planner's input format."""
+    return [(n, p.numel()) for n, p in named_parameters]
+
+
+def write_gradient_list(path, rows):
+    Path(path).write_text("".join(f"{n},{s}\n" for n, s in rows))
+
+
 def format_plan(rows) -> str:
     return "".join(f"{n},{s},{c},{k}\n" for n, s, c, k in rows)
 

@@ -24,3 +24,17 @@ def pytest_collection_modifyitems(config, items):
                 item.add_marker(pytest.mark.skip(reason="needs >= 2 GPUs"))
         elif "gpu" in item.keywords and ngpu < 1:
             item.add_marker(pytest.mark.skip(reason="needs a GPU"))
+
+
+@pytest.fixture(scope="session")
+def vgg19_gradient_list(tmp_path_factory):
+    """The planner input for VGG-19 (gradient name, element count), generated from
+    the model definition with the reference's gradient naming."""
+    from hipress_b200.models.vgg import VGG19
+    from hipress_b200.secopa import gradient_list_of, write_gradient_list
+    import torch
+    with torch.device("meta"):
+        m = VGG19()
+    path = tmp_path_factory.mktemp("secopa") / "vgg19_gradients.txt"
+    write_gradient_list(path, gradient_list_of(m.gluon_named_parameters()))
+    return path

@@ -30,11 +30,11 @@ def test_graft_entry_has_build_and_smoke():
 
 @pytest.mark.parametrize("topology,nnodes", [("PS", 4), ("PS", 8), ("PS", 16), ("RING", 4), ("RING", 8),
                                              ("RING", 16)])
-def test_secopa_cli_reproduces_the_reference_plans(tmp_path, topology, nnodes):
+def test_secopa_cli_reproduces_the_reference_plans(tmp_path, vgg19_gradient_list, topology, nnodes):
     gold = json.loads((ROOT / "tests" / "data" / "secopa_golden_plans.json").read_text())
     out = tmp_path / "plan.txt"
     rc = subprocess.run([sys.executable, "-m", "hipress_b200.secopa", "--input",
-                         str(ROOT / "tests" / "data" / "vgg19_gradients.txt"), "--output", str(out),
+                         str(vgg19_gradient_list), "--output", str(out),
                          "--topology", topology, "--nnodes", str(nnodes)], cwd=ROOT, timeout=120)
     assert rc.returncode == 0
     rows = out.read_text().splitlines()

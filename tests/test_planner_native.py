@@ -47,7 +47,7 @@ def test_uncompressed_run_has_only_plain_buckets():
     assert all(not b.fused for b in eng.buckets) and eng.backend == "allreduce"
 
 
-def test_measured_profile_compresses_only_what_pays_off_on_nvswitch():
+def test_measured_profile_compresses_only_what_pays_off_on_nvswitch(vgg19_gradient_list):
     """With coefficients fitted on the 8 x B200 box the planner keeps small
     gradients on the plain all-reduce and compresses the large FC layers."""
     from pathlib import Path
@@ -55,7 +55,7 @@ def test_measured_profile_compresses_only_what_pays_off_on_nvswitch():
     root = Path(__file__).resolve().parents[1]
     prof = CostProfile.from_json((root / "hipress_b200/secopa/profiles/b200_tbq_n8.json").read_text())
     assert prof.nodes == 8 and prof.fused_ring is not None and prof.allreduce is not None
-    rows = Planner(prof).plan(read_gradient_list(root / "tests/data/vgg19_gradients.txt"), "RING")
+    rows = Planner(prof).plan(read_gradient_list(vgg19_gradient_list), "RING")
     by = {r[0]: r for r in rows}
     assert by["vgg0_dense0_weight"][2] == "y" and by["vgg0_dense1_weight"][2] == "y"
     assert by["vgg0_conv0_weight"][2] == "n" and by["vgg0_dense2_bias"][2] == "n"
