@@ -108,3 +108,32 @@ def test_sparse_ps_through_the_optimizer_single_rank():
     assert sent[top].all()
     assert torch.allclose(-p.detach()[top], g[top])
     opt.close()
+
+
+def test_timeline_and_sm_partition_paths(tmp_path, monkeypatch):
+    """Chrome-trace timeline of bucket launches, and the green-context stream that
+    confines fused kernels to a few SMs (off by default): both paths run a step."""
+    import json
+    import hipress_b200 as hp
+    trace = tmp_path / "timeline.json"
+    monkeypatch.setenv("HIPRESS_TIMELINE", str(trace))
+    torch.manual_seed(1)
+    ps = [torch.nn.Parameter(torch.zeros(n, device="cuda")) for n in (300000, 70000, 500000, 10)]
+    named = [(f"p{i}", p) for i, p in enumerate(ps)]
+    opt = hp.DistributedOptimizer(torch.optim.SGD(ps, lr=1.0), named, algorithm="tbq", topology="ring",
+                                  comp_threshold=1024, bucket_bytes=1 << 21, partition_sms=16,
+                                  partition_ctas=32)
+    eng = opt.engine
+    assert sum(b.fused for b in eng.buckets) >= 2
+    for step in range(2):
+        for p in ps:
+            p.grad = torch.full_like(p, 0.025)
+        opt.step()
+    torch.cuda.synchronize()
+    eng.check()
+    # two steps of 0.025 with threshold 0.01: 0.01 then 0.01 sent (residual 0.03 left)
+    assert torch.allclose(ps[0].detach(), torch.full_like(ps[0], -0.02))
+    assert torch.allclose(ps[3].detach(), torch.full_like(ps[3], -0.05))
+    opt.close()
+    events = json.loads(trace.read_text())["traceEvents"]
+    assert len(events) >= 4 and all(e["dur"] >= 0 for e in events)
