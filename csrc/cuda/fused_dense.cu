@@ -475,6 +475,17 @@ __device__ __forceinline__ void decode_phase(const BucketDev& bk, const HpComm& 
   }
 }
 
+// device-side timestamps (see HpComm.trace)
+__device__ __forceinline__ void trace_mark(const HpComm& cm, int E, int which) {
+  if (cm.trace && threadIdx.x == 0) {
+    unsigned long long* t = reinterpret_cast<unsigned long long*>(cm.trace) + 4 * E;
+    const unsigned long long now = global_timer_ns();
+    if (which == 0) atomicMin(t, now);
+    else atomicMax(t + which, now);
+    if (which == 2) t[3] = cm.epoch;
+  }
+}
+
 __device__ __forceinline__ void fused_prologue(FusedSmem& sm) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) mbar_init(&sm.full[i], 1);
@@ -495,12 +506,15 @@ ring_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   const int E = cm.emulate ? (int)blockIdx.y : 0;
   uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   fused_prologue(sm);
+  trace_mark(cm, E, 0);
   encode_phases<ALG, B, HP_TOPO_RING>(bk, cm, fp, sm, R, E, status);
+  trace_mark(cm, E, 1);
   // gather: rank src finalised chunk src+1
   for (int qq = 0; qq < N; ++qq) {
     const int src = (R + qq) % N;
     decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N - 1 + src, (src + 1) % N, status);
   }
+  trace_mark(cm, E, 2);
 }
 
 // -------------------------------------------------------------------------- PS
@@ -518,9 +532,11 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   uint8_t* my_inbox = reinterpret_cast<uint8_t*>(cm.inbox[R]);
   fused_prologue(sm);
+  trace_mark(cm, E, 0);
 
   // phase 1: push
   encode_phases<ALG, B, HP_TOPO_PS>(bk, cm, fp, sm, R, E, status);
+  trace_mark(cm, E, 1);
 
   // phase 2: server for chunk R: sum the N payloads in rank order, re-encode, broadcast
   {
@@ -585,6 +601,7 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
     const int j = (R + i) % N;
     decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N + j, j, status);
   }
+  trace_mark(cm, E, 2);
 }
 
 // ------------------------------------------------------------------ host side

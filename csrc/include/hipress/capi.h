@@ -48,6 +48,10 @@ typedef struct {
   void* status;                // this rank's status words (emulate: nranks * 4 words)
   // emulation only: element strides between consecutive ranks' copies of g / r / out / sr
   int64_t emu_stride_g, emu_stride_r, emu_stride_out, emu_stride_sr;
+  // optional device-side timing of the fused dense kernels: 4 uint64 per rank played by
+  // the launch {first CTA start (min), last encode phase end (max), last CTA end (max),
+  // epoch}, %globaltimer nanoseconds; the host presets {UINT64_MAX, 0, 0, 0}.  NULL = off.
+  void* trace;
 } HpComm;
 
 #ifdef __cplusplus

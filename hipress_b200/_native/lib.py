@@ -37,7 +37,8 @@ class HpComm(C.Structure):
                 ("inbox", C.c_void_p * MAX_RANKS), ("flags", C.c_void_p * MAX_RANKS),
                 ("status", C.c_void_p),
                 ("emu_stride_g", C.c_int64), ("emu_stride_r", C.c_int64),
-                ("emu_stride_out", C.c_int64), ("emu_stride_sr", C.c_int64)]
+                ("emu_stride_out", C.c_int64), ("emu_stride_sr", C.c_int64),
+                ("trace", C.c_void_p)]
 
 
 _cpu = None

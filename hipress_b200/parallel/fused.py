@@ -42,7 +42,9 @@ class FusedDenseBucket:
     """
 
     def __init__(self, spec: AlgSpec, topology: str, sizes, nranks: int, rank: int, *,
-                 ctas: int = 64, emulate: bool = False, timeout_s: float = 2.0):
+                 ctas: int = 64, emulate: bool = False, timeout_s: float = 2.0, trace: bool = False):
+        self.trace_enabled = trace
+        self.trace = None
         if spec.sparse:
             raise ValueError("FusedDenseBucket handles onebit / tbq / terngrad")
         self.spec, self.topo = spec, TOPOLOGIES[topology.lower()]
@@ -75,6 +77,10 @@ class FusedDenseBucket:
         self.inbox_ptrs = [int(p) for p in region_ptrs]
         self.flag_ptrs = [int(p) + ioff for p in region_ptrs]
         self.status = status
+        if self.trace_enabled:
+            nr = self.nranks if self.emulate else 1
+            self.trace = torch.zeros(4 * nr, dtype=torch.int64, device=status.device)
+            self._trace_init = torch.tensor([-1, 0, 0, 0] * nr, dtype=torch.int64, device=status.device)
         return self
 
     def bind_local(self, device):
@@ -116,6 +122,7 @@ class FusedDenseBucket:
             cm.inbox[q] = self.inbox_ptrs[q]
             cm.flags[q] = self.flag_ptrs[q]
         cm.status = self.status.data_ptr()
+        self._arm_trace(cm, stream)
         if self.emulate:
             def stride(ts):
                 if ts is None or ts[0] is None:
@@ -151,11 +158,31 @@ class FusedDenseBucket:
             cm.inbox[q] = self.inbox_ptrs[q]
             cm.flags[q] = self.flag_ptrs[q]
         cm.status = self.status.data_ptr()
+        self._arm_trace(cm, stream)
         sp = self.spec
         rc = L.hp_cuda_fused_dense(self.topo, sp.alg, sp.bits, self._segs, nseg, C.byref(cm),
                                    sp.threshold, sp.seed, step, salt, self.ctas,
                                    _lib.stream_ptr(stream))
         _lib.check(rc, "fused dense launch")
+
+    def _arm_trace(self, cm, stream):
+        if self.trace is None:
+            cm.trace = None
+            return
+        if stream is not None:
+            with torch.cuda.stream(stream):
+                self.trace.copy_(self._trace_init)
+        else:
+            self.trace.copy_(self._trace_init)
+        cm.trace = self.trace.data_ptr()
+
+    def last_trace(self):
+        """Device-side timing of the last launch, per rank played by it:
+        (encode phases ms, whole kernel ms) from %globaltimer stamps."""
+        if self.trace is None:
+            return None
+        t = self.trace.cpu().view(-1, 4)
+        return [((int(r[1]) - int(r[0])) * 1e-6, (int(r[2]) - int(r[0])) * 1e-6) for r in t]
 
     def check_status(self):
         """Synchronising read of the status words; raises on a recorded timeout."""

@@ -100,6 +100,7 @@ class FusedSparseBucket:
             cm.inbox[q] = self.inbox_ptrs[q]
             cm.flags[q] = self.flag_ptrs[q]
         cm.status = self.status.data_ptr()
+        cm.trace = None
         cm.emu_stride_g, cm.emu_stride_r, cm.emu_stride_out, cm.emu_stride_sr = strides
         sp = self.spec
         us = self._us if sp.alg == DGC else None

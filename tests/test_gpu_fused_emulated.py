@@ -107,3 +107,23 @@ def test_residency_guard():
     from hipress_b200._native.lib import NativeLibraryError
     with pytest.raises(NativeLibraryError):
         b.launch([G], None, [G])
+
+
+def test_device_side_trace_reports_phase_times():
+    c = Compressor("tbq")
+    n = 1 << 22
+    b = FusedDenseBucket(c.spec, "ring", [n], 1, 0, ctas=128, trace=True).bind_local("cuda")
+    g = torch.randn(n, device="cuda")
+    r = torch.zeros(n, device="cuda")
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b.launch([g], [r], [g])
+    torch.cuda.synchronize()
+    ev0.record()
+    b.launch([g], [r], [g])
+    ev1.record()
+    torch.cuda.synchronize()
+    enc_ms, total_ms = b.last_trace()[0]
+    assert 0 < enc_ms <= total_ms
+    # the stamps bracket the kernel itself: no longer than the event-timed launch
+    assert total_ms <= ev0.elapsed_time(ev1) + 0.01
+    assert int(b.trace[3]) == b.epoch
