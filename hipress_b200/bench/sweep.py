@@ -97,8 +97,29 @@ def run_single(alg, topo, mbytes, ctas, iters, out):
     peaks = measured_peaks()
     flush = L2Flusher()
     c = Compressor(alg)
-    ef = "residual" in c.spec.state_names()
     n = mbytes * 1024 * 1024 // 4
+    if c.spec.sparse:
+        from ..parallel.fused_sparse import FusedSparseBucket
+        b = FusedSparseBucket(c.spec, [n], 1, 0, topology=topo).bind_local("cuda")
+        g = torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
+        st = c.new_state(n, "cuda")
+        acc = st["accum_v"] if "accum_v" in st else st["residual"]
+        u = st.get("momentum_u")
+        o = torch.empty(n, device="cuda")
+        sr = torch.zeros(b.chunk_elems(0), device="cuda")
+        t = time_cuda(lambda: b.launch_ptrs([g.data_ptr()], [acc.data_ptr()],
+                                            [u.data_ptr()] if u is not None else None,
+                                            [o.data_ptr()], [sr.data_ptr()]), iters=iters, flush=flush)
+        b.check_status()
+        nbytes = ((20.0 if alg == "dgc" else 12.0) + 4.0 + (8.0 if topo == "ps" else 0.0)) * n
+        gbs = nbytes / (t["median_ms"] * 1e-3) / 1e9
+        row = {"kernel": f"{topo}_{alg}_1rank", "mbytes": mbytes, "ms": round(t["median_ms"], 5),
+               "gbs": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
+               "peak_source": peaks["source"]}
+        out.append(row)
+        print(json.dumps(row), flush=True)
+        return
+    ef = "residual" in c.spec.state_names()
     b = FusedDenseBucket(c.spec, topo, [n], 1, 0, ctas=ctas).bind_local("cuda")
     g = torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
     r = torch.zeros(n, device="cuda") if ef else None
