@@ -1,6 +1,6 @@
 // Bulk-copy (TMA, untiled cp.async.bulk) pipeline helpers: global -> shared
 // memory tile prefetch with mbarrier completion.  Loads only ever read this
-// GPU's own memory and are never multicast.  Both addresses must be 16-byte
+// GPU's own memory, one destination CTA each.  Both addresses must be 16-byte
 // aligned and the size a multiple of 16 bytes; callers fall back to plain loads
 // for tiles that do not qualify.  Every mbarrier wait is bounded.
 #pragma once
