@@ -12,10 +12,13 @@ Typical use (one process per GPU, launched with ``python -m torch.distributed.ru
     loss.backward(); opt.step(); opt.zero_grad()
 """
 from .config import HipressConfig, add_hipress_args, config_from_args  # noqa: F401
-from .parallel.comm import (allreduce_, barrier, broadcast_optimizer_state,  # noqa: F401
-                            broadcast_parameters, device, init, is_initialized, local_rank, rank,
-                            shutdown, size)
+from .parallel.comm import (allgather, allreduce, allreduce_, barrier, broadcast,  # noqa: F401
+                            broadcast_optimizer_state, broadcast_parameters, device, init,
+                            is_initialized, local_rank, rank, shutdown, size)
 from .parallel.optimizer import DistributedOptimizer  # noqa: F401
+
+# the reference's MXNet front end calls the same wrapper DistributedTrainer
+DistributedTrainer = DistributedOptimizer
 from .parallel.engine import GradSyncEngine  # noqa: F401
 from .ops import Compressor, get_algorithm, algorithm_names  # noqa: F401
 

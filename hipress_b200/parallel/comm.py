@@ -94,6 +94,52 @@ def broadcast_optimizer_state(optimizer, root_rank: int = 0):
         opt.load_state_dict(obj[0])
 
 
+_syncers: dict = {}
+
+
+def allreduce(tensor: torch.Tensor, average: bool = True, name: str | None = None,
+              algorithm: str | None = None, topology: str = "ring", **algorithm_kwargs) -> torch.Tensor:
+    """Horovod-style ``allreduce``: returns the sum (or average) of `tensor` over all
+    ranks.  With ``algorithm`` set ("tbq", "onebit", ...) the tensor travels
+    compressed through the CaSync schedule; ``name`` keys the error-feedback state
+    that is kept between calls."""
+    out = tensor.clone()
+    if size() == 1 and algorithm is None:
+        return out
+    if algorithm is None:
+        return allreduce_(out, average)
+    from ..config import HipressConfig
+    from .hooks import FlatSyncer
+    key = (algorithm, topology, tuple(sorted(algorithm_kwargs.items())))
+    if key not in _syncers:
+        cfg = HipressConfig(algorithm=algorithm, topology=topology, comp_threshold=0)
+        for k, v in algorithm_kwargs.items():
+            setattr(cfg, k, v)
+        _syncers[key] = FlatSyncer(cfg)
+    flat = out.reshape(-1).float().contiguous()
+    _syncers[key].sync_(flat, key=abs(hash(name or "")) % (1 << 20))
+    if not average:
+        flat.mul_(size())
+    return flat.view_as(out).to(tensor.dtype)
+
+
+def broadcast(tensor: torch.Tensor, root_rank: int = 0) -> torch.Tensor:
+    """Horovod-style ``broadcast``: returns root's tensor on every rank."""
+    out = tensor.clone()
+    if size() > 1:
+        dist.broadcast(out, root_rank)
+    return out
+
+
+def allgather(tensor: torch.Tensor) -> torch.Tensor:
+    """Horovod-style ``allgather``: concatenation along dim 0 of every rank's tensor."""
+    if size() == 1:
+        return tensor.clone()
+    parts = [torch.empty_like(tensor) for _ in range(size())]
+    dist.all_gather(parts, tensor.contiguous())
+    return torch.cat(parts, dim=0)
+
+
 def allreduce_(t: torch.Tensor, average: bool = True):
     """Plain (uncompressed) in-place all-reduce."""
     if size() > 1:

@@ -156,3 +156,84 @@ def test_training_script_runs_end_to_end_on_cpu(tmp_path):
                  "--epochs", "2", "--fp32", "--algorithm", "onebit", "--comp-threshold", "1000",
                  "--checkpoint-dir", str(tmp_path / "ck"), "--resume"])
     assert rc == 0
+
+
+def _elastic_worker(rank, world, port2):
+    """Three ranks train; rank 2 leaves between steps; ranks 0 and 1 detect it on the
+    host, re-form a group of two and keep training with a rebuilt optimizer."""
+    import hipress_b200 as hp
+    import torch.distributed as dist
+    from hipress_b200.parallel.elastic import reform_process_group, survivors_rendezvous
+    from hipress_b200.utils.health import HealthMonitor, PeerFailure, default_store
+
+    def make(pv):
+        p = torch.nn.Parameter(pv.clone())
+        opt = hp.DistributedOptimizer(torch.optim.SGD([p], lr=1.0), [("w", p)], algorithm="none")
+        return p, opt
+
+    store = default_store()
+    mon = HealthMonitor(store, rank, world, interval_s=0.05, timeout_s=0.6)
+    p, opt = make(torch.zeros(4))
+    p.grad = torch.full((4,), float(rank + 1))
+    opt.step()                                   # average of 1,2,3 = 2
+    first = p.detach().clone()
+    dist.barrier()
+    if rank == 2:
+        mon.leave()                              # orderly exit between steps
+        time.sleep(1.5)
+        return {"first": first, "left": True}
+    dead = None
+    t0 = time.time()
+    while time.time() - t0 < 5:
+        try:
+            mon.check()
+        except PeerFailure as e:
+            dead = e.ranks
+            break
+        time.sleep(0.05)
+    assert dead == [2]
+    mon.close()
+    new_rank, new_world = survivors_rendezvous(store, rank, world, dead, generation=1)
+    reform_process_group(new_rank, new_world, port=port2, backend="gloo")
+    assert hp.size() == 2 and hp.rank() == new_rank
+    p2, opt2 = make(p.detach())                  # rebuilt for the new world size
+    p2.grad = torch.full((4,), float(rank + 1))
+    opt2.step()                                  # average of 1,2 = 1.5
+    return {"first": first, "second": p2.detach().clone(), "new": (new_rank, new_world)}
+
+
+def test_survivors_reform_a_smaller_group_and_continue():
+    from _mp import free_port
+    res = spawn(_elastic_worker, 3, free_port())
+    assert res[2]["left"]
+    for r in (0, 1):
+        assert torch.allclose(res[r]["first"], torch.full((4,), -2.0))
+        assert torch.allclose(res[r]["second"], torch.full((4,), -3.5))
+        assert res[r]["new"] == (r, 2)
+
+
+def _api_worker(rank, world):
+    import hipress_b200 as hp
+    t = torch.arange(6, dtype=torch.float32) + rank
+    s = hp.allreduce(t, average=False)
+    a = hp.allreduce(t)
+    g = hp.allgather(torch.full((2, 3), float(rank)))
+    b = hp.broadcast(torch.full((3,), float(rank)), root_rank=1)
+    big = torch.full((5000,), 0.02 * (rank + 1))
+    c1 = hp.allreduce(big, name="g", algorithm="tbq", threshold=0.01)
+    c2 = hp.allreduce(big, name="g", algorithm="tbq", threshold=0.01)
+    return {"s": s, "a": a, "g": g, "b": b, "c": (c1, c2), "alias": hp.DistributedTrainer is hp.DistributedOptimizer}
+
+
+def test_horovod_style_function_api():
+    res = spawn(_api_worker, 2)
+    for r in res:
+        assert torch.equal(r["s"], 2 * torch.arange(6, dtype=torch.float32) + 1)
+        assert torch.equal(r["a"], torch.arange(6, dtype=torch.float32) + 0.5)
+        assert r["g"].shape == (4, 3) and r["g"][:2].eq(0).all() and r["g"][2:].eq(1).all()
+        assert r["b"].eq(1).all() and r["alias"]
+        # compressed: one +threshold level per rank and call (ring: partial sums are
+        # re-quantised per hop), the rest stays in the error-feedback state
+        c1, c2 = r["c"]
+        assert torch.allclose(c1, torch.full((5000,), 0.005)) and torch.allclose(c2, c1)
+    assert torch.equal(res[0]["c"][0], res[1]["c"][0])
