@@ -151,7 +151,11 @@ class GradSyncEngine:
     # ------------------------------------------------------------------ plan
     def _make_entries(self, named):
         cfg = self.cfg
-        plan = read_plan(cfg.plan) if cfg.plan else None
+        plan = None
+        if cfg.plan == "auto":
+            plan = self._auto_plan(named)
+        elif cfg.plan:
+            plan = read_plan(cfg.plan)
         entries = []
         for i, (name, p) in enumerate(named):
             n = p.numel()
@@ -167,6 +171,28 @@ class GradSyncEngine:
                 c, k = n >= cfg.comp_threshold, 1
             entries.append(Entry(name, p, n, bool(c), max(1, int(k)), i))
         return entries
+
+    def _auto_plan(self, named):
+        """plan="auto": run the SeCoPa planner in process with a measured cost
+        profile for this world size (the shipped one, or cfg.plan_profile).  Without
+        a matching profile the size threshold decides."""
+        from pathlib import Path
+        from ..secopa.planner import CostProfile, Planner
+        cfg = self.cfg
+        path = Path(cfg.plan_profile) if cfg.plan_profile else \
+            Path(__file__).resolve().parents[1] / "secopa" / "profiles" / \
+            f"b200_{cfg.algorithm}_n{self.N}.json"
+        if not path.exists():
+            log.info("no cost profile %s: falling back to comp_threshold", path)
+            return None
+        prof = CostProfile.from_json(path.read_text())
+        if prof.nodes != self.N:
+            log.warning("cost profile %s is for %d ranks, not %d: falling back to comp_threshold",
+                        path, prof.nodes, self.N)
+            return None
+        topo = "PS" if cfg.topology == "ps" else "RING"
+        rows = Planner(prof).plan([(n, p.numel()) for n, p in named], topo)
+        return {name: (size, c == "y", k) for name, size, c, k in rows}
 
     def _check_order(self):
         """All ranks must register the same parameters in the same order."""

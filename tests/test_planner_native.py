@@ -80,3 +80,19 @@ def test_gradient_accumulation_and_unused_parameters():
     assert torch.all(unused.detach() == 0) and unused.grad is not None
     res = opt.engine.entries[0].state["residual"]
     assert torch.allclose(res, torch.full((5000,), 0.03))
+
+
+def test_plan_auto_uses_a_measured_profile(tmp_path):
+    from hipress_b200.secopa import CostProfile, LinearCost
+    prof = CostProfile(nodes=1, encode=LinearCost(), decode=LinearCost(), ring_send=LinearCost(),
+                       gather=LinearCost(), broadcast=LinearCost(),
+                       fused_ring=LinearCost(3e-9, 0.1, 0.05), allreduce=LinearCost(1e-8, 0.08, 0.05))
+    path = tmp_path / "prof.json"
+    path.write_text(prof.to_json())
+    # crossover at (0.1 - 0.08) / (1e-8 - 3e-9) ~ 2.86 M elements
+    eng = _engine([4_000_000, 1_000_000, 100], algorithm="tbq", plan="auto", plan_profile=str(path),
+                  comp_threshold=1)
+    assert [e.compress for e in eng.entries] == [True, False, False]
+    # no profile for this world size: the threshold decides
+    eng = _engine([4_000_000, 1_000_000, 100], algorithm="tbq", plan="auto", comp_threshold=500_000)
+    assert [e.compress for e in eng.entries] == [True, True, False]
