@@ -396,8 +396,9 @@ class GradSyncEngine:
                 u = e.state.get("momentum_u")
                 u_ptrs.append(None if u is None else u.data_ptr() + 4 * s.lo)
                 sst = e.server_state[s.part] if e.server_state else {}
-                if sst.get("_scratch"):
-                    sst["residual"].zero_()
+                if sst.get("_scratch"):  # on the launch stream, ordered before the kernels
+                    with torch.cuda.stream(b.stream or self.comm_stream):
+                        sst["residual"].zero_()
                 sr_ptrs.append(sst["residual"].data_ptr() if "residual" in sst else None)
             b.impl.launch_ptrs(g_ptrs, a_ptrs, u_ptrs, g_ptrs, sr_ptrs,
                                stream=b.stream or self.comm_stream)
