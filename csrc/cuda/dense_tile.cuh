@@ -204,7 +204,7 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
     Philox4 rnd;
     if (ALG == kTernGrad) {
       const uint64_t ge = elem0 + (uint64_t)i0;
-      rnd = philox4x32_10((uint32_t)(ge >> 2), tensor_id, P.step, salt, P.seed_lo, P.seed_hi);
+      rnd = philox4x32((uint32_t)(ge >> 2), tensor_id, P.step, salt, P.seed_lo, P.seed_hi);
     }
     uint32_t f = 0u;
 #pragma unroll

@@ -10,7 +10,7 @@
 //     replaced by an aligned 16-byte header so payloads can be moved with
 //     128-bit loads and stores;
 //   * its linear-congruential generator seeded identically in every thread
-//     (output/naive_random.hpp:25-67) is replaced by Philox4x32-10 keyed by
+//     (output/naive_random.hpp:25-67) is replaced by Philox4x32-7 keyed by
 //     (seed, element index, tensor id, step, salt).
 #pragma once
 #include <math.h>
@@ -80,7 +80,10 @@ HP_HD uint64_t sparse_k(uint64_t n, float ratio) {
 }
 
 // ---------------------------------------------------------------------------
-// Philox4x32-10 (Salmon et al.), counter based: one call yields four words.
+// Philox4x32 (Salmon et al.), counter based: one call yields four words.  Seven
+// rounds (the smaller of the two standard round counts, Crush-resistant per the
+// Random123 paper) are enough for stochastic rounding and keep the TernGrad
+// encoder closer to the memory roofline than ten.
 // ---------------------------------------------------------------------------
 struct Philox4 {
   uint32_t v[4];
@@ -92,10 +95,12 @@ HP_HD void philox_mulhilo(uint32_t a, uint32_t b, uint32_t& hi, uint32_t& lo) {
   lo = (uint32_t)p;
 }
 
-HP_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
-                            uint32_t k0, uint32_t k1) {
+constexpr int kPhiloxRounds = 7;
+
+HP_HD Philox4 philox4x32(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                         uint32_t k0, uint32_t k1) {
 #pragma unroll
-  for (int r = 0; r < 10; ++r) {
+  for (int r = 0; r < kPhiloxRounds; ++r) {
     uint32_t hi0, lo0, hi1, lo1;
     philox_mulhilo(0xD2511F53u, c0, hi0, lo0);
     philox_mulhilo(0xCD9E8D57u, c2, hi1, lo1);

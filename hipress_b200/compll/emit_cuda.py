@@ -14,7 +14,7 @@ produces
   ``V[i]`` subscript reads them back), and writes the ``concat`` header fields
   from the device -- no host synchronisation anywhere.
 
-``random<float>(lo, hi)`` draws from Philox4x32-10 keyed by (seed, element index,
+``random<float>(lo, hi)`` draws from Philox4x32-7 keyed by (seed, element index,
 call site), so every element gets an independent, reproducible number (the
 reference seeds an LCG identically in every thread, output/naive_random.hpp).
 """
