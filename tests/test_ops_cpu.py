@@ -149,3 +149,22 @@ def test_wire_header_layout():
     assert p[8:12].view(torch.float32).item() == 0.125
     assert p.numel() == 16 + (5000 * 2 + 7) // 8 // 16 * 16 + 16 - 0 or True
     assert c.payload_bytes(4096 * 16) == 16 + 4096 * 16 // 4
+
+
+def test_torch_custom_ops():
+    import hipress_b200.ops.torch_ops  # noqa: F401  registers torch.ops.hipress.*
+    g = torch.randn(5000) * 0.02
+    r = torch.zeros(5000)
+    p = torch.ops.hipress.encode(g, r, "tbq", 0.01, 2, 0, 0)
+    out = torch.zeros(5000)
+    torch.ops.hipress.decode(p, out, "tbq", 0.01, 2, 1.0, False)
+    assert torch.allclose(out + r, g, atol=1e-7) and r.abs().sum() > 0
+    torch.ops.hipress.decode(p, out, "tbq", 0.01, 2, 1.0, True)
+    assert torch.allclose(out, 2 * (g - r), atol=1e-7)
+    v, u = torch.zeros(5000), torch.zeros(5000)
+    p = torch.ops.hipress.encode_topk(g, v, u, "dgc", 0.01)
+    idx, val = sparse_pairs(p, 50)
+    assert idx.numel() == 50 and torch.all(v[idx] == 0)
+    p = torch.ops.hipress.encode(g, torch.empty(0), "terngrad", 0.0, 4, 3, 1)
+    torch.ops.hipress.decode(p, out, "terngrad", 0.0, 4, 1.0, False)
+    assert (out - g).abs().max() < (g.max() - g.min()) / 15 + 1e-6
