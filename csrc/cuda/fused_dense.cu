@@ -1,22 +1,23 @@
 // Fused CaSync kernels for the dense (quantising) algorithms: onebit, TBQ and
 // TernGrad.  One persistent launch synchronises a whole bucket of tensors:
 //
-//   ring : N hops of  wait -> decode incoming partial sum -> merge with the local
+//   ring : N hops of  poll incoming partial sum -> decode -> merge with the local
 //          chunk and its residual -> re-encode -> store the payload straight into
-//          the successor GPU's inbox over NVLink -> release a flag; the last hop
-//          stores the fully reduced payload into every rank's inbox, and every
-//          rank decodes all N chunks into the gradient (averaged).
+//          the successor GPU's inbox over NVLink; the last hop stores the fully
+//          reduced payload into every rank's inbox, and every rank decodes all N
+//          chunks into the gradient (averaged).
 //   PS   : encode each of the N chunks and store chunk j into owner j's inbox;
 //          the owner decodes and sums the N payloads in rank order, re-encodes
 //          with its server residual and stores the result into every inbox;
 //          every rank decodes all N chunks.
 //
-// There is no NCCL call and no separate encode or decode launch.  Payload and
-// flag traffic is plain st.global / st.release.sys to peer-mapped memory; the
-// receiver always reads its own memory.  CTA b of one rank only ever waits for
-// CTA b of other ranks, so no CTA waits on another CTA of its own GPU.  Every
-// wait is bounded: on expiry the CTA records a status word, stops waiting and
-// still runs to completion inside its own buffers.
+// There is no NCCL call and no separate encode or decode launch.  Payloads are
+// plain 8-byte stores {codes, epoch} to peer-mapped memory; the receiver polls its
+// own memory until the epoch of this launch shows up (see "transport" below).  A
+// CTA only ever waits for data produced by other GPUs, never for another CTA of
+// its own GPU.  Every wait is bounded: on expiry the thread records a status
+// word, the CTA stops waiting and still runs to completion inside its own
+// buffers.  g and r tiles are prefetched with bulk copies (pipeline.cuh).
 //
 // Reference parity: CaSync-Ring and CaSync-PS of mark14wu/hipress are selected
 // with --topo Ring|PS (README.md:45,51); their cost shape (N encodes, N decodes,
@@ -217,7 +218,7 @@ struct PhaseSpec {
   int in_slot;    // inbox slot to wait for and merge, or -1
   int ndst;       // payload goes to ranks (dst0 + q) % N, q < ndst
   int dst0;
-  int dst_slot;   // slot index inside the destination inbox (and flag row)
+  int dst_slot;   // slot index inside the destination inbox
   uint32_t salt;
 };
 
@@ -696,7 +697,8 @@ int hp_fused_dense_layout(int topo, int alg, int bits, const uint64_t* ns, int n
   return 0;
 }
 
-// uint32 flag words one rank needs for `ctas` CTAs
+// uint32 flag words reserved per rank (kept for layout compatibility; the dense
+// kernels signal inside the payload slots)
 uint64_t hp_fused_flag_words(int topo, int nranks, int ctas) {
   return (uint64_t)num_slots(topo, nranks) * (uint64_t)ctas;
 }
