@@ -25,7 +25,7 @@ class HipressConfig:
     backend: str = "auto"             # auto | fused | host | allreduce
     bucket_bytes: int = 256 << 20     # gradient bytes per fused launch
     plain_bucket_bytes: int = 32 << 20
-    ctas: int = 296                   # CTAs of a fused kernel that runs on the whole GPU
+    ctas: int = 444                   # CTAs of a fused kernel (3 per SM on a 148-SM B200)
     partition_sms: int = 0            # SMs reserved (green context) for fused kernels that overlap backward; 0 = off
     partition_ctas: int = 48          # CTAs of a fused kernel on the SM partition
     timeout_s: float = 10.0           # bound of every device-side wait
