@@ -11,7 +11,7 @@ import torch
 ROOT = Path(__file__).resolve().parents[2]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
                   "source": "fallback"}
-NVLINK_GBS_PER_DIR = 770.0  # measured peer copy on this pool (nominal 900)
+NVLINK_GBS_PER_DIR = 770.0  # measured peer-copy bandwidth per direction on B200 NVLink 5 (nominal 900)
 
 
 def measured_peaks() -> dict:
