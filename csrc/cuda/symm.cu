@@ -62,7 +62,10 @@ const char* hp_cuda_error_string(int code) {
 int hp_cuda_arena_alloc(uint64_t bytes, void** ptr) {
   cudaError_t e = cudaMalloc(ptr, bytes);
   if (e != cudaSuccess) return (int)e;
-  return (int)cudaMemset(*ptr, 0, bytes);
+  e = cudaMemset(*ptr, 0, bytes);
+  if (e != cudaSuccess) return (int)e;
+  // the zeroes must be in place before any peer can learn the address
+  return (int)cudaDeviceSynchronize();
 }
 int hp_cuda_arena_free(void* ptr) { return (int)cudaFree(ptr); }
 
