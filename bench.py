@@ -37,7 +37,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="hipress_b200", choices=["hipress_b200", "reference"])
-    ap.add_argument("--model", default="vgg19", choices=["vgg19", "resnet50", "bert_large"])
+    ap.add_argument("--model", default="vgg19",
+                    choices=["vgg19", "resnet50", "bert_large", "bert_base", "lstm", "transformer"])
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: headline config)")
     ap.add_argument("--seq-len", type=int, default=128)
     ap.add_argument("--comp-alg", default=None)

@@ -21,6 +21,9 @@ HEADLINE = {
     "vgg19": dict(batch=32, algorithm="tbq", topology="ring"),
     "resnet50": dict(batch=128, algorithm="dgc", topology="ps"),
     "bert_large": dict(batch=32, algorithm="onebit", topology="ring"),
+    "bert_base": dict(batch=32, algorithm="onebit", topology="ring"),
+    "lstm": dict(batch=80, algorithm="tbq", topology="ring"),
+    "transformer": dict(batch=64, algorithm="dgc", topology="ps"),
 }
 
 
@@ -28,7 +31,7 @@ HEADLINE = {
 class Job:
     model: torch.nn.Module
     optimizer: DistributedOptimizer
-    kind: str           # "image" | "mlm"
+    kind: str           # "image" | "mlm" | "lm"
     batch: int
     seq_len: int
     device: torch.device
@@ -41,6 +44,10 @@ class Job:
         if self.kind == "image":
             x = torch.randn(self.batch, 3, 224, 224, generator=g)
             y = torch.randint(0, 1000, (self.batch,), generator=g)
+        elif self.kind == "lm":   # next-token targets over uniform random ids
+            V = self.model.vocab_size
+            t = torch.randint(0, V, (self.batch, self.seq_len + 1), generator=g)
+            x, y = t[:, :-1].contiguous(), t[:, 1:].contiguous()
         else:
             V = self.model.c.vocab_size
             x = torch.randint(0, V, (self.batch, self.seq_len), generator=g)
@@ -132,7 +139,7 @@ def build_job(model_name: str = "vgg19", config: HipressConfig | None = None, *,
     device = device or comm.device()
     torch.manual_seed(seed)  # same initial weights on every rank
     model = get_model(name, **(model_kwargs or {})).to(device)
-    kind = "mlm" if name.startswith("bert") else "image"
+    kind = "mlm" if name.startswith("bert") else ("lm" if name in ("lstm", "transformer") else "image")
     if kind == "image" and device.type == "cuda":
         model = model.to(memory_format=torch.channels_last)
     model.train()

@@ -237,3 +237,29 @@ def test_horovod_style_function_api():
         c1, c2 = r["c"]
         assert torch.allclose(c1, torch.full((5000,), 0.005)) and torch.allclose(c2, c1)
     assert torch.equal(res[0]["c"][0], res[1]["c"][0])
+
+
+@pytest.mark.parametrize("name,kw", [
+    ("bert_base", dict(vocab_size=500, hidden=32, layers=2, heads=4, ffn=64, max_pos=32)),
+    ("lstm", dict(vocab_size=300, emb=32, hidden=32)),
+    ("transformer", dict(vocab_size=300, d_model=32, heads=4, layers=1, ffn=64, max_len=32)),
+])
+def test_sequence_model_zoo_trains_through_the_harness(name, kw):
+    import hipress_b200 as hp
+    from hipress_b200.train.harness import build_job
+    cfg = hp.HipressConfig(algorithm="tbq", topology="ring", comp_threshold=1000, threshold=1e-4)
+    job = build_job(name, cfg, batch=2, seq_len=8, dtype=torch.float32, model_kwargs=kw,
+                    device=torch.device("cpu"))
+    losses = [job.step(*job.to_device(*job.host_batch(i))).item() for i in range(3)]
+    assert all(l == l and l > 0 for l in losses)
+    assert job.optimizer.engine.stats()["compressed_elems"] > 0
+
+
+def test_full_size_models_have_the_published_parameter_counts():
+    from hipress_b200.models import get_model
+    with torch.device("meta"):
+        counts = {n: sum(p.numel() for p in get_model(n).parameters())
+                  for n in ("vgg19", "resnet50", "bert_large", "bert_base", "lstm", "transformer")}
+    assert counts["vgg19"] == 143_667_240 and counts["resnet50"] == 25_557_032
+    assert 334e6 < counts["bert_large"] < 337e6 and 109e6 < counts["bert_base"] < 111e6
+    assert 130e6 < counts["lstm"] < 140e6 and 55e6 < counts["transformer"] < 65e6
