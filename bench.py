@@ -219,7 +219,7 @@ def main():
             "data": "synthetic (N(0,1) images / uniform token ids, random-init weights)",
             "impl": "hipress_b200",
             "config": {"model": a.model, "global_batch": global_batch, "per_gpu_batch": job.batch,
-                       "seq_len": a.seq_len if job.kind == "mlm" else None,
+                       "seq_len": a.seq_len if job.kind != "image" else None,
                        "parallelism": f"dp{N}", "algorithm": cfg.algorithm, "topology": cfg.topology,
                        "comp_threshold": cfg.comp_threshold, "sync_backend": eng.backend,
                        "gradients": "fp32", "compressed_fraction":
