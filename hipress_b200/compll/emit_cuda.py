@@ -20,7 +20,7 @@ reference seeds an LCG identically in every thread, output/naive_random.hpp).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 from . import frontend as F
 from .frontend import CompileError

@@ -17,7 +17,7 @@ expression parser; the emitter works from the tree.
 from __future__ import annotations
 
 import re
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 
 class CompileError(Exception):

@@ -1,6 +1,5 @@
 """BERT-large (24 layers, hidden 1024, 16 heads, FFN 4096, vocab 30522) with a
 masked-language-model head, for the onebit / CaSync-Ring configuration."""
-import math
 
 import torch
 import torch.nn as nn

@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from .._native import lib as _lib
-from .algorithms import AlgSpec, DGC, GRADDROP, get_algorithm
+from .algorithms import AlgSpec, DGC, get_algorithm
 
 TILE = 4096
 
