@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--bucket-mb", type=int, default=None)
     ap.add_argument("--partition-sms", type=int, default=None)
     ap.add_argument("--partition-ctas", type=int, default=None)
+    ap.add_argument("--overlap-optimizer", type=int, default=None, choices=[0, 1],
+                    help="update each bucket's parameters right behind its synchronisation")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -137,6 +139,8 @@ def main():
         over["partition_sms"] = a.partition_sms
     if a.partition_ctas:
         over["partition_ctas"] = a.partition_ctas
+    if a.overlap_optimizer is not None:
+        over["overlap_optimizer"] = bool(a.overlap_optimizer)
     cfg = hp.HipressConfig.from_env(**over)
     job = build_job(a.model, cfg, batch=a.batch, seq_len=a.seq_len)
     eng = job.optimizer.engine
@@ -226,6 +230,7 @@ def main():
                            round(st["compressed_elems"] / st["total_elems"], 4),
                        "buckets": st["buckets"], "ctas": cfg.ctas, "partition_sms": cfg.partition_sms,
                        "partition_ctas": cfg.partition_ctas,
+                       "overlap_optimizer": cfg.overlap_optimizer,
                        "l2": "inputs larger than L2: weights+gradients+activations of one step "
                              "exceed the 126 MB L2 many times; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": float(loss.item()),

@@ -31,6 +31,7 @@ class HipressConfig:
     timeout_s: float = 10.0           # bound of every device-side wait
     server_residual: bool = True      # PS: error feedback on the re-encode at the owner
     overlap: bool = True              # launch buckets from gradient hooks during backward
+    overlap_optimizer: bool = False   # update a bucket's parameters right behind its synchronisation
     log_level: str = field(default_factory=lambda: os.environ.get("HIPRESS_LOG_LEVEL", "INFO"))
 
     def algorithm_kwargs(self) -> dict:
@@ -72,6 +73,8 @@ def add_hipress_args(ap: argparse.ArgumentParser) -> argparse.ArgumentParser:
     g.add_argument("--bitwidth", type=int, default=None, help="terngrad bits per element")
     g.add_argument("--ratio", type=float, default=0.001, help="dgc / graddrop send ratio")
     g.add_argument("--sync-backend", default="auto", choices=["auto", "fused", "host", "allreduce"])
+    g.add_argument("--overlap-optimizer", action="store_true",
+                   help="update each bucket's parameters right behind its synchronisation")
     return ap
 
 
@@ -79,4 +82,4 @@ def config_from_args(a) -> HipressConfig:
     return HipressConfig.from_env(
         algorithm=a.comp_alg.lower(), topology=a.topo.lower(), comp_threshold=a.comp_threshold,
         plan=a.comprplan, threshold=a.threshold, bitwidth=a.bitwidth, ratio=a.ratio,
-        backend=a.sync_backend)
+        backend=a.sync_backend, overlap_optimizer=getattr(a, "overlap_optimizer", False) or None)

@@ -143,6 +143,9 @@ class GradSyncEngine:
             for e in self.entries:
                 self._hooks.append(e.param.register_post_accumulate_grad_hook(self._on_grad))
         self._begin()
+        # called as on_bucket_done(bucket) with the bucket's averaged gradients
+        # next in order on the current stream (DistributedOptimizer's overlapped step)
+        self.on_bucket_done = None
         self.launch_count = 0
         self.bytes_sent = 0
         self.timeline = Timeline()
@@ -363,6 +366,9 @@ class GradSyncEngine:
             if tok is not None:
                 self.timeline.end(tok, st, step=self.step_no, fused=True,
                                   elems=sum(e.numel for e in b.entries))
+            if self.on_bucket_done is not None:
+                with torch.cuda.stream(st):
+                    self.on_bucket_done(b)
             return
         if self.on_cuda:
             st = b.stream or self.comm_stream
@@ -383,6 +389,8 @@ class GradSyncEngine:
             if tok is not None:
                 self.timeline.end(tok, torch.cuda.current_stream(), step=self.step_no,
                                   fused=b.fused, elems=sum(e.numel for e in b.entries))
+            if b.fused and self.on_bucket_done is not None:
+                self.on_bucket_done(b)
 
     def _launch_fused(self, b: Bucket):
         grads = {id(e): self._grad(e) for e in b.entries}
@@ -461,6 +469,8 @@ class GradSyncEngine:
                 for b in self.buckets:
                     if not b.fused:
                         self._finish_plain(b)
+                        if self.on_bucket_done is not None:
+                            self.on_bucket_done(b)
                 if self.arena is not None:
                     self._poll_status()
             torch.cuda.current_stream().wait_stream(self.comm_stream)
@@ -468,6 +478,8 @@ class GradSyncEngine:
             for b in self.buckets:
                 if not b.fused:
                     self._finish_plain(b)
+                    if self.on_bucket_done is not None:
+                        self.on_bucket_done(b)
         self.step_no += 1
         self._begin()
 

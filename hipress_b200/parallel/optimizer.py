@@ -33,6 +33,46 @@ class DistributedOptimizer:
         self.engine = GradSyncEngine(list(named_parameters), cfg, group=group,
                                      backward_passes_per_step=backward_passes_per_step)
         self._synchronized = False
+        self._bucket_opts = None
+        if cfg.overlap_optimizer:
+            self._make_bucket_optimizers()
+
+    # ------------------------------------------------ overlapped parameter update
+    def _make_bucket_optimizers(self):
+        """One optimizer per synchronisation bucket, of the wrapped optimizer's class,
+        stepped on the communication stream right behind the bucket's kernel, so the
+        update of the layers that finish backward first hides behind the rest of
+        backward.  The per-bucket optimizers share the wrapped optimizer's ``state``
+        mapping (its ``state_dict`` stays complete) and re-read its hyper-parameters
+        at every step (learning-rate schedulers keep working).  Anything that needs
+        all gradients before the update (clipping, a closure) needs the option off."""
+        src_group = {}
+        for g in self.optimizer.param_groups:
+            for p in g["params"]:
+                src_group[p] = g
+        cls = type(self.optimizer)
+        self._bucket_opts = {}
+        for b in self.engine.buckets:
+            groups = {}
+            for e in b.entries:
+                g = src_group.get(e.param)
+                if g is None:
+                    raise ValueError(f"{e.name} is synchronised but not owned by the optimizer")
+                groups.setdefault(id(g), (g, []))[1].append(e.param)
+            pgs = [{**{k: v for k, v in g.items() if k != "params"}, "params": ps}
+                   for g, ps in groups.values()]
+            bo = cls(pgs)
+            bo.state = self.optimizer.state
+            self._bucket_opts[b.index] = (bo, [g for g, _ in groups.values()])
+        self.engine.on_bucket_done = self._step_bucket
+
+    def _step_bucket(self, bucket):
+        bo, sources = self._bucket_opts[bucket.index]
+        for pg, src in zip(bo.param_groups, sources):
+            for k, v in src.items():
+                if k != "params":
+                    pg[k] = v
+        bo.step()
 
     # Horovod API
     def synchronize(self):
@@ -43,6 +83,10 @@ class DistributedOptimizer:
         if not self._synchronized:
             self.engine.synchronize()
         self._synchronized = False
+        if self._bucket_opts is not None:
+            if closure is not None:
+                raise ValueError("overlap_optimizer does not support a closure")
+            return None  # every bucket was stepped behind its synchronisation
         return self.optimizer.step(closure)
 
     def zero_grad(self, set_to_none: bool = True):

@@ -170,3 +170,42 @@ def test_ddp_comm_hook_keeps_replicas_identical():
     for a, b in zip(res[0]["grads"], res[1]["grads"]):
         assert torch.equal(a, b)
     assert res[0]["resid"] > 0  # error feedback is active
+
+
+# ----------------------------------------------------------------------------
+def _run_overlapped_update(rank, world, overlap):
+    import hipress_b200 as hp
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 96), torch.nn.ReLU(), torch.nn.Linear(96, 48),
+                                torch.nn.ReLU(), torch.nn.Linear(48, 8))
+    inner = torch.optim.SGD([{"params": model[0].parameters()},
+                             {"params": list(model[2].parameters()) + list(model[4].parameters()),
+                              "weight_decay": 1e-3}], lr=0.5, momentum=0.9)
+    sched = torch.optim.lr_scheduler.StepLR(inner, step_size=2, gamma=0.5)
+    opt = hp.DistributedOptimizer(inner, list(model.named_parameters()), algorithm="tbq",
+                                  topology="ring", comp_threshold=1024, threshold=0.001,
+                                  bucket_bytes=16 << 10, overlap_optimizer=overlap)
+    g = torch.Generator().manual_seed(7 + rank)
+    for step in range(5):
+        x = torch.randn(16, 64, generator=g)
+        opt.zero_grad()
+        model(x).square().mean().backward()
+        opt.step()
+        sched.step()
+    sd = opt.state_dict()["optimizer"]
+    return {"params": [p.detach().clone() for p in model.parameters()],
+            "momenta": [sd["state"][i]["momentum_buffer"].clone() for i in sorted(sd["state"])],
+            "buckets": len(opt.engine.buckets)}
+
+
+def test_overlapped_optimizer_step_matches_plain_step():
+    """Stepping each bucket right behind its synchronisation gives the parameters,
+    momenta and schedule of one step() after synchronize()."""
+    plain = _spawn(_run_overlapped_update, 2, False)
+    over = _spawn(_run_overlapped_update, 2, True)
+    assert plain[0]["buckets"] > 1
+    assert len(over[0]["momenta"]) == 6
+    for a, b in zip(plain[0]["params"] + plain[0]["momenta"], over[0]["params"] + over[0]["momenta"]):
+        assert torch.equal(a, b)
+    for a, b in zip(over[0]["params"], over[1]["params"]):
+        assert torch.equal(a, b)
