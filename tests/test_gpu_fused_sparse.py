@@ -137,3 +137,38 @@ def test_timeline_and_sm_partition_paths(tmp_path, monkeypatch):
     opt.close()
     events = json.loads(trace.read_text())["traceEvents"]
     assert len(events) >= 4 and all(e["dur"] >= 0 for e in events)
+
+
+def test_overlapped_optimizer_step_on_the_communication_stream():
+    """overlap_optimizer updates each bucket behind its fused kernel, during backward;
+    parameters and momenta equal those of a single step() after synchronize()."""
+    import hipress_b200 as hp
+
+    def run(overlap):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(512, 1024), torch.nn.ReLU(),
+                                    torch.nn.Linear(1024, 768), torch.nn.ReLU(),
+                                    torch.nn.Linear(768, 16)).cuda()
+        inner = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, fused=True)
+        opt = hp.DistributedOptimizer(inner, list(model.named_parameters()), algorithm="tbq",
+                                      topology="ring", comp_threshold=1024, threshold=1e-4,
+                                      bucket_bytes=3 << 20, overlap_optimizer=overlap)
+        assert opt.engine.backend == "fused" and sum(b.fused for b in opt.engine.buckets) >= 2
+        gen = torch.Generator(device="cuda").manual_seed(5)
+        for _ in range(4):
+            x = torch.randn(64, 512, device="cuda", generator=gen)
+            opt.zero_grad()
+            model(x).square().mean().backward()
+            opt.step()
+        torch.cuda.synchronize()
+        opt.engine.check()
+        sd = inner.state_dict()["state"]
+        out = [p.detach().clone() for p in model.parameters()] + \
+              [sd[i]["momentum_buffer"].clone() for i in sorted(sd)]
+        opt.close()
+        return out
+
+    plain, over = run(False), run(True)
+    assert len(plain) == len(over) == 12
+    for a, b in zip(plain, over):
+        assert torch.equal(a, b)
