@@ -277,14 +277,14 @@ class Emitter:
                 raise CompileError(f"statement not supported in a lambda: {type(st).__name__}")
         return "\n".join(out)
 
-    def lambda_fn(self, s: Sym) -> str:
+    def lambda_fn(self, s: Sym, qual: str = "__device__ __forceinline__") -> str:
         lam: F.Lambda = s.expr
         local = {n for _, n in lam.params}
         self._counter = lam.params[0][1] if lam.params else "zero"
         ret = "uint32_t" if lam.ret.is_subbyte() else C_TYPES[lam.ret.name]
         params = ", ".join(f"{C_TYPES[t.name]} l_{n}" for t, n in lam.params)
         body = self.stmts(lam.body, local, lam.ret.is_subbyte())
-        return (f"__device__ __forceinline__ {ret} fn_{s.name}(const Ctx& c"
+        return (f"{qual} {ret} fn_{s.name}(const Ctx& c"
                 f"{', ' if params else ''}{params}) {{\n{body}\n}}\n")
 
     # ---------------------------------------------------------- pieces
@@ -513,6 +513,7 @@ __global__ void __launch_bounds__(256) {name}_map{idx}_kernel({self.kernel_param
     def body_source(self) -> str:
         """The generated kernels (``-b``)."""
         name = self.fn.name
+        self.rand_sites = 0  # call sites are numbered per emission: both targets agree
         lambdas = "\n".join(self.lambda_fn(s) for s in self.syms.values() if s.kind == "lambda")
         maps = "\n".join(self.map_kernel(i, t, m, i == len(self.maps) - 1)
                          for i, (t, m) in enumerate(self.maps))
@@ -649,6 +650,11 @@ int compll_{name}({sig}) {{
     def uses_library(self) -> bool:
         return any(st[0] in ("topk", "scatter") for st in self.stages)
 
+    def host_source(self) -> str:
+        """The CPU target: the same function as sequential C++ (``-t cpu``)."""
+        from .emit_host import host_source
+        return host_source(self)
+
     def register_source(self, framework: str = "torch") -> str:
         """Python registration (``-r -f torch``): binds the launcher to torch tensors."""
         name = self.fn.name
@@ -665,7 +671,10 @@ int compll_{name}({sig}) {{
                 conv.append(f"{pname}")
                 ctypes_sig.append({"float": "C.c_float", "int": "C.c_int32", "uint": "C.c_uint32"}
                                   .get(ty.name, "C.c_uint8"))
-        return f'''"""Generated by hipress_b200.compll: PyTorch binding of {name}."""
+        vecs = [pname for ty, pname in self.fn.params if ty.vector]
+        return f'''"""Generated by hipress_b200.compll: PyTorch binding of {name}.  Tensors on the
+CPU run the generated C++ (lib{name}_cpu.so), CUDA tensors the sm_100a kernels
+(lib{name}.so)."""
 import ctypes as C
 import os
 
@@ -673,7 +682,9 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _lib = None
+_cpu = None
 _scratch = {{}}
+_SIG = [{", ".join(ctypes_sig)}]
 
 
 def _load():
@@ -681,19 +692,41 @@ def _load():
     if _lib is None:
         _lib = C.CDLL(os.path.join(_HERE, "lib{name}.so"))
         _lib.compll_{name}.restype = C.c_int
-        _lib.compll_{name}.argtypes = [{", ".join(ctypes_sig)}, C.c_void_p, C.c_uint64, C.c_void_p]
+        _lib.compll_{name}.argtypes = _SIG + [C.c_void_p, C.c_uint64, C.c_void_p]
         _lib.compll_{name}_scratch_bytes.restype = C.c_uint64
     return _lib
 
 
+def _load_cpu():
+    global _cpu
+    if _cpu is None:
+        _cpu = C.CDLL(os.path.join(_HERE, "lib{name}_cpu.so"))
+        _cpu.compll_{name}_cpu.restype = C.c_int
+        _cpu.compll_{name}_cpu.argtypes = _SIG + [C.c_uint64]
+    return _cpu
+
+
 def {name}({", ".join(args)}, seed=0, stream=None):
-    """In-place op: vectors are torch CUDA tensors allocated by the caller."""
+    """In-place op: vectors are contiguous torch tensors allocated by the caller,
+    all on one device."""
+    vectors = ({", ".join(vecs)},)
+    if any(not t.is_contiguous() for t in vectors):
+        raise ValueError("{name}: tensors must be contiguous")
+    if len({{t.device for t in vectors}}) != 1:
+        raise ValueError("{name}: tensors must share one device")
+    if not vectors[0].is_cuda:
+        rc = _load_cpu().compll_{name}_cpu({", ".join(conv)}, seed)
+        if rc != 0:
+            raise RuntimeError(f"{name}: error {{rc}}")
+        return
     lib = _load()
-    dev = torch.cuda.current_device()
-    if dev not in _scratch:
-        _scratch[dev] = torch.zeros(int(lib.compll_{name}_scratch_bytes()), dtype=torch.uint8, device="cuda")
-    st = (stream or torch.cuda.current_stream()).cuda_stream
-    rc = lib.compll_{name}({", ".join(conv)}, _scratch[dev].data_ptr(), seed, st)
+    dev = vectors[0].device.index
+    with torch.cuda.device(dev):
+        if dev not in _scratch:
+            _scratch[dev] = torch.zeros(int(lib.compll_{name}_scratch_bytes()), dtype=torch.uint8,
+                                        device="cuda")
+        st = (stream or torch.cuda.current_stream()).cuda_stream
+        rc = lib.compll_{name}({", ".join(conv)}, _scratch[dev].data_ptr(), seed, st)
     if rc != 0:
         raise RuntimeError(f"{name}: CUDA error {{rc}}")
 '''
