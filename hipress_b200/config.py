@@ -15,7 +15,7 @@ class HipressConfig:
     algorithm: str = "tbq"            # onebit | tbq | terngrad | dgc | graddrop | none
     topology: str = "ring"            # ring | ps
     comp_threshold: int = 262144      # gradients with fewer elements are not compressed
-    plan: str | None = None           # SeCoPa plan file (overrides comp_threshold), or "auto"
+    plan: str | None = None           # SeCoPa plan file (overrides comp_threshold), "auto" or "auto:bucketed"
     plan_profile: str | None = None   # cost profile for plan="auto" (default: shipped B200 profile)
     threshold: float = 0.01           # tbq
     bitwidth: int | None = None       # terngrad

@@ -155,8 +155,8 @@ class GradSyncEngine:
     def _make_entries(self, named):
         cfg = self.cfg
         plan = None
-        if cfg.plan == "auto":
-            plan = self._auto_plan(named)
+        if cfg.plan in ("auto", "auto:bucketed"):
+            plan = self._auto_plan(named, bucketed=cfg.plan.endswith("bucketed"))
         elif cfg.plan:
             plan = read_plan(cfg.plan)
         entries = []
@@ -175,10 +175,11 @@ class GradSyncEngine:
             entries.append(Entry(name, p, n, bool(c), max(1, int(k)), i))
         return entries
 
-    def _auto_plan(self, named):
+    def _auto_plan(self, named, bucketed=False):
         """plan="auto": run the SeCoPa planner in process with a measured cost
         profile for this world size (the shipped one, or cfg.plan_profile).  Without
-        a matching profile the size threshold decides."""
+        a matching profile the size threshold decides.  plan="auto:bucketed" decides
+        jointly for the bucket sizes of this engine instead of gradient by gradient."""
         from pathlib import Path
         from ..secopa.planner import CostProfile, Planner
         cfg = self.cfg
@@ -194,7 +195,11 @@ class GradSyncEngine:
                         path, prof.nodes, self.N)
             return None
         topo = "PS" if cfg.topology == "ps" else "RING"
-        rows = Planner(prof).plan([(n, p.numel()) for n, p in named], topo)
+        grads = [(n, p.numel()) for n, p in named]
+        if bucketed:
+            rows = Planner(prof).plan_bucketed(grads, topo, cfg.bucket_bytes, cfg.plain_bucket_bytes)
+        else:
+            rows = Planner(prof).plan(grads, topo)
         return {name: (size, c == "y", k) for name, size, c, k in rows}
 
     def _check_order(self):

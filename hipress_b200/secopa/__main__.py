@@ -16,6 +16,9 @@ def main(argv=None):
     ap.add_argument("--nnodes", type=int, default=16, help="cluster size")
     ap.add_argument("--profile", default="reference",
                     help="'reference' or a JSON file written by hipress_b200.secopa.profiler")
+    ap.add_argument("--bucketed", action="store_true",
+                    help="decide jointly for a bucketed runtime (measured profiles only)")
+    ap.add_argument("--bucket-mb", type=int, default=256, help="--bucketed: gradient MB per fused launch")
     a = ap.parse_args(argv)
     if a.profile == "reference":
         prof = reference_profile(a.nnodes)
@@ -24,7 +27,10 @@ def main(argv=None):
             prof = CostProfile.from_json(f.read())
         if prof.nodes != a.nnodes:
             raise SystemExit(f"profile was measured for {prof.nodes} nodes, not {a.nnodes}")
-    rows = Planner(prof).plan(read_gradient_list(a.input), a.topology)
+    if a.bucketed:
+        rows = Planner(prof).plan_bucketed(read_gradient_list(a.input), a.topology, a.bucket_mb << 20)
+    else:
+        rows = Planner(prof).plan(read_gradient_list(a.input), a.topology)
     with open(a.output, "w") as f:
         f.write(format_plan(rows))
 

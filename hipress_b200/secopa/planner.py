@@ -5,7 +5,7 @@ uncompressed with the cost of the compressed CaSync path, over every partition
 count K = 1..N, and writes one plan row ``name,size,y|n,K``.
 
 Cost terms are ``cost(x) = slope*x + intercept`` floored at ``floor`` (x in fp32
-elements).  Two kinds of profile exist:
+elements), or tables of measured points.  Two kinds of profile exist:
 
 * ``reference_profile(N)``: the coefficients the HiPress authors fitted on their
   cluster (src/SeCoPa/SeCoPa.py:25-39 of mark14wu/hipress), available for
@@ -47,6 +47,32 @@ class LinearCost:
         return self.slope * x + self.intercept
 
 
+@dataclass(frozen=True)
+class TableCost:
+    """Measured (elements, milliseconds) points, interpolated linearly.  Below the
+    first point the first time applies (launch latency); beyond the last one the
+    last segment's slope continues.  End-to-end terms are not straight lines on an
+    NVSwitch box (latency floor, then a knee where the kernel fills the GPU, then
+    bandwidth), and a single least-squares line misplaces the crossover."""
+    points: tuple = ()
+
+    def __post_init__(self):
+        pts = tuple(sorted((float(x), float(y)) for x, y in self.points))
+        if not pts:
+            raise ValueError("a cost table needs at least one point")
+        object.__setattr__(self, "points", pts)
+
+    def __call__(self, x: float) -> float:
+        pts = self.points
+        if x <= pts[0][0] or len(pts) == 1:
+            return pts[0][1]
+        for (x0, y0), (x1, y1) in zip(pts, pts[1:]):
+            if x <= x1:
+                return y0 + (y1 - y0) * (x - x0) / (x1 - x0)
+        (x0, y0), (x1, y1) = pts[-2], pts[-1]
+        return y1 + max(0.0, (y1 - y0) / (x1 - x0)) * (x - x1)
+
+
 @dataclass
 class CostProfile:
     """All cost terms for one cluster size."""
@@ -60,9 +86,17 @@ class CostProfile:
     comp_ratio: float = 1.0 / 16
     # measured end-to-end terms (B200 profiles); when present they replace the
     # composition of primitives above
-    fused_ring: LinearCost | None = None
-    fused_ps: LinearCost | None = None
-    allreduce: LinearCost | None = None
+    fused_ring: LinearCost | TableCost | None = None
+    fused_ps: LinearCost | TableCost | None = None
+    allreduce: LinearCost | TableCost | None = None
+    # gradients smaller than this stay uncompressed whatever the costs say: a
+    # rank's chunk would be under one tile, and quantising tiny tensors (biases,
+    # norms) buys no time at all
+    min_compress_elems: int = 0
+    # compress only when it is at least this fraction cheaper: keeps decisions in the
+    # launch-latency region, where both fitted lines are flat and differ by noise,
+    # on the plain path (0 reproduces the reference's strict comparison)
+    margin: float = 0.0
     source: str = "reference"
 
     def to_json(self) -> str:
@@ -72,7 +106,9 @@ class CostProfile:
     def from_json(text: str) -> "CostProfile":
         d = json.loads(text)
         def lc(v):
-            return None if v is None else LinearCost(**v)
+            if v is None:
+                return None
+            return TableCost(tuple(map(tuple, v["points"]))) if "points" in v else LinearCost(**v)
         keys = ("encode", "decode", "ring_send", "gather", "broadcast", "merge", "fused_ring",
                 "fused_ps", "allreduce")
         return CostProfile(**{k: (lc(v) if k in keys else v) for k, v in d.items()})
@@ -127,6 +163,8 @@ class Planner:
     def compressed_cost(self, size: int, topology: str):
         p, N = self.p, self.p.nodes
         fused = p.fused_ps if topology == "PS" else p.fused_ring
+        if isinstance(fused, TableCost):
+            return fused(size), 1  # measured whole: partitions do not change a persistent launch
         if fused is not None:
             # one persistent launch per bucket: partitions only shorten the
             # per-hop pipeline fill, modelled as the intercept shared by K parts
@@ -152,11 +190,50 @@ class Planner:
         """-> ('y'|'n', K)"""
         topology = "PS" if topology.upper() == "PS" else "RING"
         orig, k_orig = self.uncompressed_cost(size, topology)
+        if size < self.p.min_compress_elems:
+            return "n", k_orig
         comp, k_comp = self.compressed_cost(size, topology)
-        return ("y", k_comp) if orig > comp else ("n", k_orig)
+        return ("y", k_comp) if orig * (1.0 - self.p.margin) > comp else ("n", k_orig)
 
     def plan(self, gradients: Iterable[tuple[str, int]], topology: str):
         return [(name, size, *self.decide(size, topology)) for name, size in gradients]
+
+    # -- joint decision for a bucketed runtime ----------------------------
+    def _set_cost(self, cost, total: float, bucket_elems: float) -> float:
+        """Cost of `total` elements moved in launches of at most `bucket_elems`."""
+        if total <= 0:
+            return 0.0
+        full, rest = divmod(total, bucket_elems)
+        return full * cost(bucket_elems) + (cost(rest) if rest > 0 else 0.0)
+
+    def plan_bucketed(self, gradients: Iterable[tuple[str, int]], topology: str,
+                      bucket_bytes: int = 256 << 20, plain_bucket_bytes: int = 32 << 20):
+        """Plan for a runtime that batches gradients into buckets (one fused launch
+        per compressed bucket, one all-reduce per plain bucket), where the
+        per-gradient comparison charges every gradient a launch latency it does not
+        pay.  Needs measured end-to-end terms.  Picks the size threshold T that
+        minimises  fused(sum of sizes >= T) + allreduce(sum of sizes < T), both
+        split into buckets; T never falls below ``min_compress_elems`` and
+        compressing must beat leaving everything plain by the profile's margin."""
+        p = self.p
+        topology = "PS" if topology.upper() == "PS" else "RING"
+        fused = p.fused_ps if topology == "PS" else p.fused_ring
+        if fused is None or p.allreduce is None:
+            raise ValueError("plan_bucketed needs a profile with measured fused and all-reduce terms")
+        grads = list(gradients)
+        sizes = sorted({s for _, s in grads if s >= max(1, p.min_compress_elems)}, reverse=True)
+        fb, pb = bucket_bytes / 4.0, plain_bucket_bytes / 4.0
+        total = float(sum(s for _, s in grads))
+        all_plain = self._set_cost(p.allreduce, total, pb)
+        best_cost, best_t = all_plain, None
+        comp = 0.0
+        for t in sizes:                       # thresholds from the largest size down
+            comp += float(sum(s for _, s in grads if s == t))
+            c = self._set_cost(fused, comp, fb) + self._set_cost(p.allreduce, total - comp, pb)
+            if c < best_cost and c < all_plain * (1.0 - p.margin):
+                best_cost, best_t = c, t
+        return [(name, size, "y" if best_t is not None and size >= best_t else "n", 1)
+                for name, size in grads]
 
 
 # ------------------------------------------------------------------ plan files

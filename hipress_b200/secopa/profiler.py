@@ -23,7 +23,11 @@ import json
 
 import torch
 
-from .planner import CostProfile, LinearCost
+from .planner import CostProfile, LinearCost, TableCost
+
+
+TILE = 4096   # elements per tile of the wire format: a rank's chunk should hold at least one
+MARGIN = 0.1  # run-to-run spread of the sub-0.1 ms timings the fits' floors come from
 
 
 def fit_linear(xs, ys) -> LinearCost:
@@ -94,42 +98,71 @@ def profile(algorithm="tbq", nnodes=8, min_elems=1 << 14, max_elems=1 << 26, ite
                 t = {k: v / nnodes for k, v in t.items()}
                 add(topo, n, t)
                 del b, G, R
-    fits = {k: (fit_linear(*v) if v[0] else None) for k, v in pts.items()}
+    fits = {k: ((fit_linear if k in ("encode", "decode") else fit_table)(*v) if v[0] else None)
+            for k, v in pts.items()}
     send = LinearCost(4.0 / 770e9 * 1e3, 0.003, 0.003)  # 770 GB/s measured peer copy, ~3 us latency
     return CostProfile(nodes=nnodes, encode=fits["encode"], decode=fits["decode"], ring_send=send,
                        gather=send, broadcast=send, comp_ratio=comp.payload_bytes(1 << 20) / (4 << 20),
                        fused_ring=fits["ring"], fused_ps=fits["ps"], allreduce=fits["allreduce"],
+                       margin=MARGIN, min_compress_elems=nnodes * TILE,
                        source=f"measured on {torch.cuda.get_device_name()} ({'real' if real else 'emulated'} ranks)")
 
 
-def profile_from_sweep(path, algorithm="tbq") -> CostProfile:
+def fit_table(xs, ys) -> TableCost:
+    """The measured points themselves (one time per size: the smallest seen)."""
+    best = {}
+    for x, y in zip(xs, ys):
+        best[x] = min(y, best.get(x, y))
+    return TableCost(tuple(sorted(best.items())))
+
+
+def profile_from_sweep(path, algorithm="tbq", ops_path=None, fit="table") -> CostProfile:
     """Fit a profile from the rows a multi-GPU run of
     ``hipress_b200.bench.sweep_multi`` wrote (fused ring / PS and NCCL all-reduce
-    times per size, measured on real ranks)."""
+    times per size, measured on real ranks).  ``ops_path``: rows of
+    ``hipress_b200.bench.sweep --what ops`` (stand-alone encode / decode times) for
+    the encode and decode terms; without it the TBQ kernel coefficients stand in."""
+    from ..ops import Compressor
     rows = [r for r in json.load(open(path)) if r["alg"] == algorithm]
     if not rows:
         raise ValueError(f"no rows for {algorithm} in {path}")
     n = rows[0]["n_gpus"]
 
-    def fit(key, topo=None):
+    def term(key, topo=None):
         pts = [(r["bytes"] / 4.0, r[key]) for r in rows
                if key in r and r[key] and (topo is None or r["topo"] == topo)]
         pts = sorted(set(pts))
-        return fit_linear([p[0] for p in pts], [p[1] for p in pts]) if pts else None
+        fn = fit_table if fit == "table" else fit_linear
+        return fn([p[0] for p in pts], [p[1] for p in pts]) if pts else None
 
     send = LinearCost(4.0 / 770e9 * 1e3, 0.003, 0.003)
-    enc = LinearCost(1.65e-9, 0.0208, 0.0196)   # stand-alone kernels, one B200 (profile())
+    enc = LinearCost(1.65e-9, 0.0208, 0.0196)   # stand-alone TBQ kernels, one B200 (profile())
     dec = LinearCost(1.26e-9, 0.0178, 0.0183)
+    note = ""
+    if ops_path:
+        ops = [r for r in json.load(open(ops_path)) if r["alg"] == algorithm]
+        for op in ("encode", "decode"):
+            pts = sorted({(r["bytes"] / 4.0, r["ms"]) for r in ops if r["op"] == op})
+            if pts:
+                f = fit_linear([x for x, _ in pts], [y for _, y in pts])
+                enc, dec = (f, dec) if op == "encode" else (enc, f)
+        note = ", encode/decode from the kernel sweep"
+    ratio = Compressor(algorithm).payload_bytes(1 << 20) / float(4 << 20)
     return CostProfile(nodes=n, encode=enc, decode=dec, ring_send=send, gather=send, broadcast=send,
-                       comp_ratio=1.0 / 16, fused_ring=fit("fused_ms", "ring"),
-                       fused_ps=fit("fused_ms", "ps"), allreduce=fit("allreduce_ms"),
-                       source=f"fitted from {n}-GPU sweep rows ({algorithm})")
+                       comp_ratio=ratio, fused_ring=term("fused_ms", "ring"),
+                       fused_ps=term("fused_ms", "ps"), allreduce=term("allreduce_ms"), margin=MARGIN,
+                       min_compress_elems=n * TILE,
+                       source=f"fitted from {n}-GPU sweep rows ({algorithm}){note}")
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description="measure B200 cost coefficients for SeCoPa")
     ap.add_argument("--from-sweep", default=None,
                     help="fit from a sweep_multi JSON instead of measuring now")
+    ap.add_argument("--from-ops-sweep", default=None,
+                    help="with --from-sweep: kernel sweep JSON for the encode / decode terms")
+    ap.add_argument("--fit", default="table", choices=["table", "linear"],
+                    help="with --from-sweep: keep the measured points (interpolated) or fit one line")
     ap.add_argument("--algorithm", default="tbq")
     ap.add_argument("--nnodes", type=int, default=8)
     ap.add_argument("--min-elems", type=int, default=1 << 14)
@@ -139,7 +172,7 @@ def main(argv=None):
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args(argv)
     if a.from_sweep:
-        prof = profile_from_sweep(a.from_sweep, a.algorithm)
+        prof = profile_from_sweep(a.from_sweep, a.algorithm, a.from_ops_sweep, a.fit)
         with open(a.output, "w") as f:
             f.write(prof.to_json())
         print(a.output)
