@@ -74,6 +74,34 @@ uint64_t hp_sparse_payload_bytes(uint64_t kmax) { return sparse_payload_bytes(km
 uint64_t hp_sparse_k(uint64_t n, float ratio) { return sparse_k(n, ratio); }
 int hp_tile_elems() { return kTile; }
 
+// Integrity check of a received payload before it is decoded.  Dense: pass the
+// element count n the receiver expects and kmax = 0; sparse: bits = 0 and the
+// capacity kmax the buffer was laid out for.  Returns 0 or the first mismatch:
+//   1 buffer shorter than the format needs   2 algorithm id   3 bit width
+//   4 element count   5 tile size / flags    6 pair count above capacity or n
+//   7 pair index out of range
+int hp_payload_check(const uint8_t* payload, uint64_t payload_bytes, int alg, int bits, uint64_t n,
+                     uint64_t kmax) {
+  if (payload_bytes < 16) return 1;
+  const WireHeader* h = reinterpret_cast<const WireHeader*>(payload);
+  const bool sparse = alg == kDgc || alg == kGradDrop;
+  if (h->alg != (uint8_t)alg) return 2;
+  if (h->bitwidth != (uint8_t)(sparse ? 0 : bits)) return 3;
+  if (h->n != (uint32_t)n) return 4;
+  if (sparse) {
+    if (payload_bytes < sparse_payload_bytes(kmax)) return 1;
+    if (h->b > kmax || h->b > n) return 6;
+    const uint32_t* idx = reinterpret_cast<const uint32_t*>(payload + 16);
+    for (uint32_t j = 0; j < h->b; ++j)
+      if (idx[j] >= n) return 7;
+    return 0;
+  }
+  if (!dense_args_ok(alg, bits)) return 3;
+  if (payload_bytes < dense_payload_bytes(alg, bits, n)) return 1;
+  if (h->b != (uint32_t)kTile || h->flags != (dense_meta_floats(alg) ? 1 : 0)) return 5;
+  return 0;
+}
+
 // x = g (+ decode(in_payload)) (+ r);  payload = Q(x);  r = x - decode(payload)
 int hp_cpu_dense_encode(int alg, int bits, const float* g, float* r,
                         const uint8_t* in_payload, uint8_t* out, uint64_t n, float tau,

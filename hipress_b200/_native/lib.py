@@ -94,6 +94,7 @@ def cpu():
 
 # symbols added by later translation units of the CPU library (planner, scheduler)
 _CPU_OPTIONAL: dict = {
+    "hp_payload_check": (C.c_int, C.c_void_p, C.c_uint64, C.c_int, C.c_int, C.c_uint64, C.c_uint64),
     "hp_plan_buckets": (C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64,
                         C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                         C.c_void_p, C.c_void_p, C.c_void_p),
@@ -154,12 +155,15 @@ def cuda():
 _CUDA_OPTIONAL: dict = {}
 
 
-def check(code: int, what: str = "native call"):
-    """Raise on a non-zero return code of an ``hp_*`` function."""
+def check(code: int, what: str = "native call", device_call: bool = True):
+    """Raise on a non-zero return code of an ``hp_*`` function (``device_call``:
+    positive codes are CUDA runtime errors; otherwise the CPU library's own)."""
     if code == 0:
         return
     if code < 0:
         raise NativeLibraryError(f"{what}: {ERR_NAMES.get(code, code)}")
+    if not device_call:
+        raise NativeLibraryError(f"{what}: invalid argument or payload (code {code})")
     msg = cuda().hp_cuda_error_string(code).decode() if _cuda is not None else str(code)
     raise NativeLibraryError(f"{what}: CUDA error {code}: {msg}")
 

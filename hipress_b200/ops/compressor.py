@@ -25,6 +25,10 @@ def _c(t):
     return None if t is None else t.data_ptr()
 
 
+class PayloadError(RuntimeError):
+    """A received payload does not match the format its receiver expects."""
+
+
 class Compressor:
     def __init__(self, spec: AlgSpec | str, **overrides):
         self.spec = get_algorithm(spec, **overrides) if isinstance(spec, str) else spec
@@ -84,7 +88,7 @@ class Compressor:
             rc = _lib.cpu().hp_cpu_dense_encode(sp.alg, sp.bits, _c(g), _c(r), _c(incoming), _c(out),
                                                 n, sp.threshold, sp.seed, step, salt, tensor_id,
                                                 elem_offset)
-        _lib.check(rc, f"{sp.name} encode")
+        _lib.check(rc, f"{sp.name} encode", device_call=g.is_cuda)
         return out
 
     def _encode_sparse(self, g, state, incoming, out, update, workspace, kmax, stream, max_ctas):
@@ -116,7 +120,7 @@ class Compressor:
         if incoming is not None:
             raise ValueError("merge incoming sparse payloads with decode(accumulate=True)")
         rc = L.hp_cpu_sparse_select(sp.alg, _c(a), _c(u), n, k, _c(out), kmax)
-        _lib.check(rc, f"{sp.name} select")
+        _lib.check(rc, f"{sp.name} select", device_call=False)
         return out
 
     def update_state(self, g, state, stream=None):
@@ -166,8 +170,30 @@ class Compressor:
         else:
             rc = _lib.cpu().hp_cpu_dense_decode(sp.alg, sp.bits, _c(payload), _c(out), n,
                                                 sp.threshold, scale, 1 if accumulate else 0)
-        _lib.check(rc, f"{sp.name} decode")
+        _lib.check(rc, f"{sp.name} decode", device_call=out.is_cuda)
         return out
+
+    _PAYLOAD_FAULTS = {1: "buffer shorter than the format needs", 2: "algorithm id", 3: "bit width",
+                       4: "element count", 5: "tile size or flags", 6: "pair count above capacity",
+                       7: "pair index out of range"}
+
+    def check_payload(self, payload, n, kmax=None):
+        """Integrity check of a received payload against what this compressor would
+        have produced for ``n`` elements (header fields, sizes, sparse indices);
+        raises :class:`PayloadError` naming the first mismatch.  The payload is read
+        on the host: for a CUDA tensor this copies and synchronises, so the host
+        transport verifies device payloads only when asked to."""
+        sp = self.spec
+        p = payload if not payload.is_cuda else payload.cpu()
+        p = p.contiguous()
+        if sp.sparse:
+            kmax = self.kmax(n) if kmax is None else kmax
+            rc = _lib.cpu().hp_payload_check(_c(p), p.numel(), sp.alg, 0, n, kmax)
+        else:
+            rc = _lib.cpu().hp_payload_check(_c(p), p.numel(), sp.alg, sp.bits, n, 0)
+        if rc:
+            raise PayloadError(f"{sp.name} payload for {n} elements is corrupt: "
+                               f"{self._PAYLOAD_FAULTS.get(rc, rc)}")
 
 
 def sparse_pairs(payload: torch.Tensor, kmax: int):

@@ -13,11 +13,15 @@ import torch.distributed as dist
 _state = {"init": False, "rank": 0, "size": 1, "local_rank": 0, "own_pg": False, "device": None}
 
 
-def init(backend: str | None = None, timeout_s: float = 600.0):
+def init(backend: str | None = None, timeout_s: float | None = None):
     """Join the job described by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR /
-    MASTER_PORT (as set by ``torch.distributed.run``)."""
+    MASTER_PORT (as set by ``torch.distributed.run``).  ``timeout_s`` (default 600,
+    or HIPRESS_PG_TIMEOUT_S) bounds every collective and message of the process
+    group: a peer that never joins ends the call with an error."""
     if _state["init"]:
         return
+    if timeout_s is None:
+        timeout_s = float(os.environ.get("HIPRESS_PG_TIMEOUT_S", "600"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank_ = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -13,13 +13,14 @@ Reference parity: CaSync-Ring / CaSync-PS, ``--topo Ring|PS``
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import torch
 import torch.distributed as dist
 
 from .._native import lib as _lib
-from ..ops.compressor import Compressor
+from ..ops.compressor import Compressor, PayloadError
 from .simulate import chunk_elems, chunk_range
 
 
@@ -33,8 +34,15 @@ class SegView:
 
 
 class HostSchedule:
-    def __init__(self, comp: Compressor, topology: str, group=None):
+    def __init__(self, comp: Compressor, topology: str, group=None, verify: bool | None = None):
+        """``verify``: check the header, sizes and indices of every received chunk
+        payload before it is decoded and raise ``PayloadError`` naming hop and
+        source (a corrupted or misrouted message must not be folded into the
+        gradients).  Default: on for host tensors, where the check reads 16 bytes
+        in place; off for device tensors (it would copy and synchronise) unless
+        HIPRESS_VERIFY=1."""
         self.comp, self.topology, self.group = comp, topology.lower(), group
+        self.verify = verify
         self.N = dist.get_world_size(group) if dist.is_initialized() else 1
         self.R = dist.get_rank(group) if dist.is_initialized() else 0
         self._bufs = {}
@@ -63,6 +71,22 @@ class HostSchedule:
             b = torch.zeros(nbytes, dtype=torch.uint8, device=device)
             self._bufs[key] = b
         return b[:nbytes]
+
+    def _verify(self, segs, offs, msg, chunk, what):
+        """Integrity check of one received message: every segment's payload for `chunk`."""
+        on = self.verify
+        if on is None:
+            on = (not msg.is_cuda) or os.environ.get("HIPRESS_VERIFY") == "1"
+        if not on:
+            return
+        for s, (o, nb, kmax) in zip(segs, offs):
+            lo, hi = chunk_range(s.g.numel(), self.N, chunk)
+            if hi <= lo:
+                continue
+            try:
+                self.comp.check_payload(msg[o:o + nb], hi - lo, kmax=kmax)
+            except PayloadError as e:
+                raise PayloadError(f"rank {self.R}, {what}, segment {s.seg_id}: {e}") from None
 
     def _global(self, r):
         return r if self.group is None else dist.get_global_rank(self.group, r)
@@ -114,6 +138,8 @@ class HostSchedule:
             c = (R - hop) % N
             out = send[hop & 1]
             inc = recv[hop & 1] if hop > 0 else None
+            if inc is not None:
+                self._verify(segs, offs, inc, c, f"ring hop {hop} from rank {(R - 1) % N}")
             for s, (o, nb, kmax) in zip(segs, offs):
                 self._encode_chunk(s, c, hop, None if inc is None else inc[o:o + nb],
                                    out[o:o + nb], kmax, step, salt)
@@ -127,6 +153,8 @@ class HostSchedule:
             gathered = [cur]
         for src in range(N):
             c = (src + 1) % N
+            if src != R:
+                self._verify(segs, offs, gathered[src], c, f"ring gather from rank {src}")
             for s, (o, nb, kmax) in zip(segs, offs):
                 self._decode_chunk(s, c, gathered[src][o:o + nb], kmax)
 
@@ -154,6 +182,9 @@ class HostSchedule:
         else:
             inbox[0] = push[0]
         pull = self._buf(("pull",), total, dev)
+        for q in range(N):
+            if q != R:
+                self._verify(segs, offs, inbox[q], R, f"PS push from rank {q}")
         for s, (o, nb, kmax) in zip(segs, offs):
             lo, hi = chunk_range(s.g.numel(), N, R)
             if hi <= lo:
@@ -180,5 +211,7 @@ class HostSchedule:
         else:
             gathered = [pull]
         for j in range(N):
+            if j != R:
+                self._verify(segs, offs, gathered[j], j, f"PS pull from rank {j}")
             for s, (o, nb, kmax) in zip(segs, offs):
                 self._decode_chunk(s, j, gathered[j][o:o + nb], kmax)

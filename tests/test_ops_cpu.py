@@ -147,7 +147,8 @@ def test_wire_header_layout():
     assert p[0:4].view(torch.int32).item() == 5000
     assert p[4].item() == 2 and p[5].item() == 2
     assert p[8:12].view(torch.float32).item() == 0.125
-    assert p.numel() == 16 + (5000 * 2 + 7) // 8 // 16 * 16 + 16 - 0 or True
+    assert p.numel() == 16 + (1250 + 15) // 16 * 16     # header + 2 bits per element, 16-byte aligned
+    assert p[12:16].view(torch.int32).item() == 4096    # tile size
     assert c.payload_bytes(4096 * 16) == 16 + 4096 * 16 // 4
 
 
