@@ -126,7 +126,7 @@ class Emitter:
                     self.order.append(name)
             self.maps.append((name, v))
             self.stages.append(("map", len(self.maps) - 1))
-        elif isinstance(v, F.Call) and v.fn in ("topk", "scatter"):
+        elif isinstance(v, F.Call) and v.fn in ("topk", "scatter", "scatter_add"):
             # library-lowered stages: exact top-k selection / sparse scatter of the
             # run-time library (radix select in shared memory, block compaction)
             if tgt.kind != "param_vector":
@@ -136,8 +136,9 @@ class Emitter:
                                                           (v.args[0],) + tuple(v.args[2:])):
                     raise CompileError("topk(vector, k[, companion]) takes vector names", st.line)
             elif len(v.args) != 2 or not isinstance(v.args[0], F.Name):
-                raise CompileError("scatter(payload, scale) takes a payload vector and a scale", st.line)
-            self.stages.append((v.fn, name, v))
+                raise CompileError(f"{v.fn}(payload, scale) takes a payload vector and a scale", st.line)
+            # scatter overwrites the target (zero, then place); scatter_add merges into it
+            self.stages.append(("topk" if v.fn == "topk" else "scatter", name, v))
         elif isinstance(v, F.Concat):
             if tgt.kind != "param_vector":
                 raise CompileError("the left-hand side of concat must be a function parameter", st.line)
@@ -592,7 +593,7 @@ namespace compll_gen_{name} {{
     if (n_{src} < 16) return -1;
     const uint64_t kmax = (n_{src} - 16) / 8;   // capacity of the payload buffer in pairs
     int rc = hp_cuda_sparse_decode(reinterpret_cast<const uint8_t*>(p_{src}), p_{target}, n_{target},
-                                   kmax, (float)({sexp}), 0, stream);
+                                   kmax, (float)({sexp}), {1 if call.fn == "scatter_add" else 0}, stream);
     if (rc) return rc;
   }}""")
                 continue

@@ -110,7 +110,7 @@ def _library_stage(em: Emitter, st) -> str:
     if (n_{src} < 16) return -1;
     const uint64_t kmax = (n_{src} - 16) / 8;   // capacity of the payload buffer in pairs
     int rc = hp_cpu_sparse_decode(reinterpret_cast<const uint8_t*>(p_{src}), p_{target}, n_{target},
-                                  kmax, (float)({sexp}), 0);
+                                  kmax, (float)({sexp}), {1 if call.fn == "scatter_add" else 0});
     if (rc) return rc;
   }}"""
 

@@ -264,3 +264,51 @@ def test_generated_graddrop_and_dgc_use_the_library_topk(tmp_path, device):
     mask = torch.ones(n, dtype=torch.bool, device=device)
     mask[top] = False
     assert torch.allclose(v[mask], v_ref[mask], rtol=1e-6) and torch.allclose(u[mask], u_ref[mask], rtol=1e-6)
+
+
+def test_decode_accumulate_for_every_format(tmp_path):
+    """The fused decode + merge of each wire format, generated from the DSL and run
+    on the CPU target: target += decode(payload) * weight."""
+    device = "cpu"
+    n = 20011
+    torch.manual_seed(11)
+    g = torch.randn(n) * 0.02
+    base = torch.randn(n)
+    # onebit
+    enc = _load(tmp_path, "OnebitEncode", device=device)
+    dec = _load(tmp_path, "OnebitDecode", device=device)
+    acc = _load(tmp_path, "OnebitDecodeAccumulate", device=device)
+    comp = torch.zeros(4 + (n + 7) // 8, dtype=torch.uint8)
+    enc(g, torch.zeros(n), comp)
+    plain = torch.empty(n)
+    dec(comp, plain)
+    out = base.clone()
+    acc(comp, out, 0.125)
+    assert torch.allclose(out, base + 0.125 * plain, atol=1e-7)
+    # terngrad, 4 bits
+    enc = _load(tmp_path, "TernGradEncode", device=device)
+    dec = _load(tmp_path, "TernGradDecode", device=device)
+    acc = _load(tmp_path, "TernGradDecodeAccumulate", device=device)
+    comp = torch.zeros(10 + (n + 1) // 2, dtype=torch.uint8)
+    enc(g, comp, 4, seed=5)
+    dec(comp, plain)
+    out = base.clone()
+    acc(comp, out, 0.5)
+    assert torch.allclose(out, base + 0.5 * plain, atol=1e-7)
+    # sparse (GradDrop payload), scatter_add keeps what the target held
+    import math
+    ratio = 0.01
+    k = max(int(math.ceil(torch.tensor(ratio, dtype=torch.float32).item() * n)), 1)
+    enc = _load(tmp_path, "GradDropEncode", device=device)
+    acc = _load(tmp_path, "SparseDecodeAccumulate", device=device)
+    comp = torch.zeros(16 + 2 * ((4 * k + 15) // 16 * 16), dtype=torch.uint8)
+    enc(g, torch.zeros(n), comp, ratio)
+    out = base.clone()
+    acc(comp, out, 0.25)
+    top = torch.topk(g.abs(), k).indices
+    want = base.clone()
+    want[top] += 0.25 * g[top]
+    assert torch.allclose(out, want, atol=1e-7)
+    em = generate((PSE / "SparseDecodeAccumulate.pse").read_text())
+    assert "n_gradient,\n" in em.wrapper_source() and ", 1, stream)" in em.wrapper_source()
+    assert ", 0, stream)" in generate((PSE / "GradDropDecode.pse").read_text()).wrapper_source()
