@@ -12,9 +12,10 @@ Typical use (one process per GPU, launched with ``python -m torch.distributed.ru
     loss.backward(); opt.step(); opt.zero_grad()
 """
 from .config import HipressConfig, add_hipress_args, config_from_args  # noqa: F401
-from .parallel.comm import (allgather, allreduce, allreduce_, barrier, broadcast,  # noqa: F401
-                            broadcast_optimizer_state, broadcast_parameters, device, init,
-                            is_initialized, local_rank, rank, shutdown, size)
+from .parallel.comm import (allgather, allgather_object, allreduce, allreduce_, barrier,  # noqa: F401
+                            broadcast, broadcast_object, broadcast_optimizer_state,
+                            broadcast_parameters, device, init, is_initialized, local_rank,
+                            local_size, rank, shutdown, size)
 from .parallel.optimizer import DistributedOptimizer  # noqa: F401
 
 # the reference's MXNet front end calls the same wrapper DistributedTrainer

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import datetime
 import os
+import zlib
 
 import torch
 import torch.distributed as dist
@@ -68,6 +69,12 @@ def local_rank() -> int:
     return _state["local_rank"]
 
 
+def local_size() -> int:
+    """Ranks on this machine (LOCAL_WORLD_SIZE as set by ``torch.distributed.run``;
+    every rank of the job on a single box)."""
+    return int(os.environ.get("LOCAL_WORLD_SIZE", _state["size"]))
+
+
 def device() -> torch.device:
     return _state["device"] or torch.device("cuda" if torch.cuda.is_available() else "cpu")
 
@@ -121,7 +128,8 @@ def allreduce(tensor: torch.Tensor, average: bool = True, name: str | None = Non
             setattr(cfg, k, v)
         _syncers[key] = FlatSyncer(cfg)
     flat = out.reshape(-1).float().contiguous()
-    _syncers[key].sync_(flat, key=abs(hash(name or "")) % (1 << 20))
+    # a stable key: str hashes differ between processes and runs
+    _syncers[key].sync_(flat, key=zlib.crc32((name or "").encode()) % (1 << 20))
     if not average:
         flat.mul_(size())
     return flat.view_as(out).to(tensor.dtype)
@@ -136,12 +144,43 @@ def broadcast(tensor: torch.Tensor, root_rank: int = 0) -> torch.Tensor:
 
 
 def allgather(tensor: torch.Tensor) -> torch.Tensor:
-    """Horovod-style ``allgather``: concatenation along dim 0 of every rank's tensor."""
+    """Horovod-style ``allgather``: concatenation along dim 0 of every rank's tensor;
+    the first dimension may differ between ranks, the others must agree."""
     if size() == 1:
         return tensor.clone()
-    parts = [torch.empty_like(tensor) for _ in range(size())]
-    dist.all_gather(parts, tensor.contiguous())
-    return torch.cat(parts, dim=0)
+    t = tensor.contiguous()
+    rows = torch.tensor([t.shape[0] if t.dim() else 1], dtype=torch.int64, device=t.device)
+    every = [torch.empty_like(rows) for _ in range(size())]
+    dist.all_gather(every, rows)
+    counts = [int(r.item()) for r in every]
+    if len(set(counts)) == 1:
+        parts = [torch.empty_like(t) for _ in range(size())]
+        dist.all_gather(parts, t)
+        return torch.cat([p.reshape(-1, *t.shape[1:]) if not t.dim() else p for p in parts], dim=0)
+    most = max(counts)
+    padded = torch.zeros((most, *t.shape[1:]), dtype=t.dtype, device=t.device)
+    padded[:t.shape[0]] = t
+    parts = [torch.empty_like(padded) for _ in range(size())]
+    dist.all_gather(parts, padded)
+    return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)
+
+
+def broadcast_object(obj, root_rank: int = 0):
+    """Horovod-style ``broadcast_object``: root's picklable object on every rank."""
+    if size() == 1:
+        return obj
+    box = [obj if rank() == root_rank else None]
+    dist.broadcast_object_list(box, src=root_rank)
+    return box[0]
+
+
+def allgather_object(obj) -> list:
+    """Horovod-style ``allgather_object``: every rank's picklable object, by rank."""
+    if size() == 1:
+        return [obj]
+    out = [None] * size()
+    dist.all_gather_object(out, obj)
+    return out
 
 
 def allreduce_(t: torch.Tensor, average: bool = True):

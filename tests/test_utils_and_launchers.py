@@ -222,7 +222,11 @@ def _api_worker(rank, world):
     big = torch.full((5000,), 0.02 * (rank + 1))
     c1 = hp.allreduce(big, name="g", algorithm="tbq", threshold=0.01)
     c2 = hp.allreduce(big, name="g", algorithm="tbq", threshold=0.01)
-    return {"s": s, "a": a, "g": g, "b": b, "c": (c1, c2), "alias": hp.DistributedTrainer is hp.DistributedOptimizer}
+    ragged = hp.allgather(torch.full((rank + 1, 2), float(rank)))     # 1 row from rank 0, 2 from rank 1
+    objs = hp.allgather_object({"rank": rank})
+    root = hp.broadcast_object({"from": rank}, root_rank=1)
+    return {"s": s, "a": a, "g": g, "b": b, "c": (c1, c2), "ragged": ragged, "objs": objs, "root": root,
+            "local_size": hp.local_size(), "alias": hp.DistributedTrainer is hp.DistributedOptimizer}
 
 
 def test_horovod_style_function_api():
@@ -232,6 +236,9 @@ def test_horovod_style_function_api():
         assert torch.equal(r["a"], torch.arange(6, dtype=torch.float32) + 0.5)
         assert r["g"].shape == (4, 3) and r["g"][:2].eq(0).all() and r["g"][2:].eq(1).all()
         assert r["b"].eq(1).all() and r["alias"]
+        assert r["ragged"].shape == (3, 2) and r["ragged"][:, 0].tolist() == [0.0, 1.0, 1.0]
+        assert r["objs"] == [{"rank": 0}, {"rank": 1}] and r["root"] == {"from": 1}
+        assert r["local_size"] == 2
         # compressed: one +threshold level per rank and call (ring: partial sums are
         # re-quantised per hop), the rest stays in the error-feedback state
         c1, c2 = r["c"]
