@@ -98,5 +98,9 @@ def build(force: bool = False, verbose: bool = False) -> dict:
     return out
 
 
-if __name__ == "__main__":
+def main():
     print(build(force="--force" in sys.argv, verbose=True))
+
+
+if __name__ == "__main__":
+    main()
