@@ -30,6 +30,7 @@ class HipressConfig:
     partition_ctas: int = 48          # CTAs of a fused kernel on the SM partition
     timeout_s: float = 10.0           # bound of every device-side wait
     server_residual: bool = True      # PS: error feedback on the re-encode at the owner
+    hierarchical: str = "auto"        # job on several machines: auto | on | off (see GradSyncEngine)
     overlap: bool = True              # launch buckets from gradient hooks during backward
     overlap_optimizer: bool = False   # update a bucket's parameters right behind its synchronisation
     log_level: str = field(default_factory=lambda: os.environ.get("HIPRESS_LOG_LEVEL", "INFO"))

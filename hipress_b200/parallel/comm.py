@@ -51,6 +51,7 @@ def shutdown():
     if _state["own_pg"] and dist.is_initialized():
         dist.destroy_process_group()
     _state.update(init=False, rank=0, size=1, local_rank=0, own_pg=False)
+    _state.pop("hier", None)
 
 
 def is_initialized() -> bool:
@@ -73,6 +74,56 @@ def local_size() -> int:
     """Ranks on this machine (LOCAL_WORLD_SIZE as set by ``torch.distributed.run``;
     every rank of the job on a single box)."""
     return int(os.environ.get("LOCAL_WORLD_SIZE", _state["size"]))
+
+
+def group_size(group=None) -> int:
+    return size() if group is None else dist.get_world_size(group)
+
+
+def group_rank(group=None) -> int:
+    return rank() if group is None else dist.get_rank(group)
+
+
+def hierarchy():
+    """How the job's ranks sit on machines.  Returns ``None`` for a job on one
+    machine (or a world of one) and otherwise a dict with
+
+    * ``node_of``: machine index of every rank, ``nodes``: number of machines,
+    * ``local_size``: ranks per machine, or ``None`` when machines differ,
+    * ``local_group`` / ``cross_group``: this rank's machine-local group and the
+      group of the ranks with its local index on every machine (only for equal
+      machine sizes above 1).
+
+    Machines are told apart by host name; ``HIPRESS_NODE_ID`` overrides it (one
+    machine can then stand in for several).  Collective over the job: every rank
+    must call it at the same point.  The result is cached."""
+    if "hier" in _state:
+        return _state["hier"]
+    out = None
+    if size() > 1:
+        import socket
+        ident = os.environ.get("HIPRESS_NODE_ID") or socket.gethostname()
+        ids = [None] * size()
+        dist.all_gather_object(ids, ident)
+        order = list(dict.fromkeys(ids))
+        if len(order) > 1:
+            node_of = [order.index(i) for i in ids]
+            members = [[r for r, n in enumerate(node_of) if n == k] for k in range(len(order))]
+            sizes = {len(m) for m in members}
+            out = {"node_of": node_of, "nodes": len(order), "local_size": None,
+                   "local_group": None, "cross_group": None}
+            if len(sizes) == 1 and len(members[0]) > 1:
+                per = len(members[0])
+                me = rank()
+                # every rank creates every group, in the same order
+                locals_ = [dist.new_group(m) for m in members]
+                crosses = [dist.new_group([m[j] for m in members]) for j in range(per)]
+                out.update(local_size=per, local_group=locals_[node_of[me]],
+                           cross_group=crosses[members[node_of[me]].index(me)])
+            elif len(sizes) == 1:
+                out["local_size"] = 1
+    _state["hier"] = out
+    return out
 
 
 def device() -> torch.device:

@@ -14,6 +14,16 @@ threshold) and the number of partitions K.  Compressed gradients go through
                baseline);
 * ``allreduce``: no compression, plain all-reduce (the uncompressed baseline).
 
+A job that spans several machines (the reference's usual deployment: one GPU per
+machine over Ethernet, README.md:29-45) is handled in two ways.  With one rank per
+machine the ``host`` schedule carries the compressed payloads over the network
+transport.  With several ranks per machine the engine works hierarchically: the
+fused kernels (or the host schedule on CPU ranks) average a bucket inside the
+machine, every local rank then takes one 1/L shard of each tensor through a
+compressed exchange with the ranks of the same local index on the other
+machines, and an all-gather inside the machine hands every rank the full result.
+Peer-mapped memory never leaves a machine.
+
 Uncompressed gradients always use a bucketed plain all-reduce, as in the
 reference ("PS-Lite and NCCL are used", README.md:153 of mark14wu/hipress).
 Every rank launches buckets in the same fixed order; the order of parameter names
@@ -81,6 +91,11 @@ class Bucket:
     flat: torch.Tensor | None = None
     work: object = None
     stream: object = None
+    # hierarchical mode: per segment (lo, hi, state, owner state) of this rank's shard,
+    # and the staging buffers of the all-gather inside the machine
+    outer: list = field(default_factory=list)
+    ag_in: torch.Tensor | None = None
+    ag_out: list = field(default_factory=list)
 
 
 def _flat(t: torch.Tensor) -> torch.Tensor:
@@ -108,7 +123,24 @@ class GradSyncEngine:
         self.passes = max(1, int(backward_passes_per_step))
         if not comm.is_initialized():
             comm.init()
-        self.N, self.R, self.group = comm.size(), comm.rank(), group
+        self.world_group = group          # plain buckets and consistency checks span the whole job
+        self.outer = None                 # hierarchical mode: the exchange between machines
+        force_host = False
+        if group is None and cfg.hierarchical != "off" and comm.size() > 1 and \
+                cfg.algorithm not in ("none", None, ""):
+            h = comm.hierarchy()
+            if h is not None and h["local_group"] is not None:
+                group = h["local_group"]
+                self.outer = {"group": h["cross_group"], "nodes": h["nodes"], "local": h["local_size"]}
+            elif h is not None and cfg.backend in ("auto", "fused"):
+                if cfg.hierarchical == "on" and h["local_size"] != 1:
+                    raise ValueError("hierarchical synchronisation needs the same number of ranks "
+                                     "on every machine")
+                log.info("ranks sit on %d machines: compressed payloads travel over the host "
+                         "transport", h["nodes"])
+                force_host = True         # peer-mapped memory does not cross machines
+        self.N, self.R, self.group = comm.group_size(group), comm.group_rank(group), group
+        self.world, self.world_rank = comm.group_size(self.world_group), comm.group_rank(self.world_group)
         named = [(n, p) for n, p in named_parameters if p.requires_grad]
         if not named:
             raise ValueError("no trainable parameters")
@@ -118,6 +150,8 @@ class GradSyncEngine:
         self.comp = Compressor(get_algorithm(cfg.algorithm, **cfg.algorithm_kwargs())) \
             if self.compress else None
         backend = cfg.backend
+        if force_host:
+            backend = "host"
         if backend == "auto":
             backend = "fused" if self.on_cuda else "host"
         if backend == "fused" and not self.on_cuda:
@@ -204,14 +238,15 @@ class GradSyncEngine:
 
     def _check_order(self):
         """All ranks must register the same parameters in the same order."""
-        if self.N == 1:
+        if self.world == 1:
             return
         mine = [(e.name, e.numel, e.compress, e.partitions) for e in self.entries]
-        every = [None] * self.N
-        dist.all_gather_object(every, mine, group=self.group)
+        every = [None] * self.world
+        dist.all_gather_object(every, mine, group=self.world_group)
         for q, other in enumerate(every):
             if other != mine:
-                raise RuntimeError(f"rank {self.R} and rank {q} disagree on the gradient list or plan")
+                raise RuntimeError(f"rank {self.world_rank} and rank {q} disagree on the gradient "
+                                   "list or plan")
 
     def _make_buckets(self):
         """Bucket planning is done by the native planner (csrc/cpu/planner.cpp):
@@ -295,9 +330,11 @@ class GradSyncEngine:
         elif fused_buckets and not use_fused_kernels:
             self._host = HostSchedule(self.comp, cfg.topology, self.group)
         for b in self.buckets:
-            if not b.fused and self.N > 1:
+            if not b.fused and self.world > 1:
                 b.flat = torch.zeros(sum(e.numel for e in b.entries), dtype=torch.float32,
                                      device=self.device)
+        if self.outer is not None:
+            self._setup_outer(fused_buckets)
 
     def _make_partition_stream(self):
         """Stream bound to a green context of cfg.partition_sms SMs; falls back to
@@ -368,6 +405,9 @@ class GradSyncEngine:
             st.wait_event(ev)
             tok = self.timeline.begin(f"bucket{b.index}", st) if self.timeline.enabled else None
             self._launch_fused(b)
+            if self.outer is not None:
+                with torch.cuda.stream(st):
+                    self._between_machines(b)
             if tok is not None:
                 self.timeline.end(tok, st, step=self.step_no, fused=True,
                                   elems=sum(e.numel for e in b.entries))
@@ -389,6 +429,8 @@ class GradSyncEngine:
                 if self.timeline.enabled else None
             if b.fused:
                 self._launch_fused(b)
+                if self.outer is not None:
+                    self._between_machines(b)
             else:
                 self._launch_plain(b)
             if tok is not None:
@@ -441,19 +483,78 @@ class GradSyncEngine:
                                      e.server_state[s.part] if e.server_state else {}, s.seg_id))
             self._host.sync(views, step=self.step_no)
 
+    # ------------------------------------------------- between machines
+    def _setup_outer(self, fused_buckets):
+        """State of the exchange between machines: this rank's 1/L shard of every
+        segment has its own error-feedback state (and owner-side state for PS)."""
+        from .simulate import chunk_range
+        o = self.outer
+        spec = self.comp.spec
+        if spec.sparse:
+            # the momentum correction already ran inside the machine; between
+            # machines the shard only needs a plain error-feedback accumulator
+            o["comp"] = Compressor(get_algorithm("graddrop", ratio=spec.ratio))
+        else:
+            o["comp"] = self.comp
+        o["sched"] = HostSchedule(o["comp"], self.cfg.topology, o["group"])
+        M = o["nodes"]
+        for b in fused_buckets:
+            b.outer = []
+            for s in b.segs:
+                lo, hi = chunk_range(s.n, self.N, self.R)
+                m = max(hi - lo, 0)
+                st = o["comp"].new_state(m, self.device) if m else {}
+                sst = {}
+                if m and self.cfg.topology == "ps" and self.cfg.server_residual and \
+                        (o["comp"].spec.sparse or "residual" in o["comp"].spec.state_names()):
+                    sst = {"residual": torch.zeros(chunk_elems(m, M), dtype=torch.float32,
+                                                   device=self.device)}
+                b.outer.append((lo, hi, st, sst))
+            per = sum(chunk_elems(s.n, self.N) for s in b.segs)
+            b.ag_in = torch.zeros(per, dtype=torch.float32, device=self.device)
+            b.ag_out = [torch.zeros(per, dtype=torch.float32, device=self.device) for _ in range(self.N)]
+
+    def _between_machines(self, b: Bucket):
+        """Second and third stage of a bucket in hierarchical mode: compressed
+        exchange of this rank's shards with the other machines, then an all-gather
+        of the shards inside the machine.  Runs on the current stream, behind the
+        bucket's synchronisation inside the machine."""
+        from .simulate import chunk_range
+        o = self.outer
+        flats = [_flat(self._grad(s.entry))[s.lo:s.hi] for s in b.segs]
+        views = [SegView(f[lo:hi], st, sst, s.seg_id)
+                 for f, s, (lo, hi, st, sst) in zip(flats, b.segs, b.outer) if hi > lo]
+        if views:
+            o["sched"].sync(views, step=self.step_no, salt=1 << 16)
+        off = 0
+        for f, s, (lo, hi, _, _) in zip(flats, b.segs, b.outer):
+            if hi > lo:
+                b.ag_in[off:off + hi - lo].copy_(f[lo:hi])
+            off += chunk_elems(s.n, self.N)
+        dist.all_gather(b.ag_out, b.ag_in, group=self.group)
+        for q in range(self.N):
+            if q == self.R:
+                continue
+            off = 0
+            for f, s in zip(flats, b.segs):
+                lo, hi = chunk_range(s.n, self.N, q)
+                if hi > lo:
+                    f[lo:hi].copy_(b.ag_out[q][off:off + hi - lo])
+                off += chunk_elems(s.n, self.N)
+
     def _launch_plain(self, b: Bucket):
-        if self.N == 1:
+        if self.world == 1:
             return
         grads = [self._grad(e) for e in b.entries]
         torch.cat([g.reshape(-1) for g in grads], out=b.flat)
-        b.work = dist.all_reduce(b.flat, group=self.group, async_op=True)
+        b.work = dist.all_reduce(b.flat, group=self.world_group, async_op=True)
 
     def _finish_plain(self, b: Bucket):
-        if self.N == 1 or b.work is None:
+        if self.world == 1 or b.work is None:
             return
         b.work.wait()
         b.work = None
-        b.flat.div_(self.N)
+        b.flat.div_(self.world)
         off = 0
         for e in b.entries:
             e.param.grad.copy_(b.flat[off:off + e.numel].view_as(e.param.grad))
@@ -528,8 +629,16 @@ class GradSyncEngine:
                         d[f"server_{k}.{i}"] = v.detach().cpu().clone()
             d["step"] = self.step_no
             out[e.name] = d
-        return {"world_size": self.N, "rank": self.R, "algorithm": self.cfg.algorithm,
-                "topology": self.cfg.topology, "step": self.step_no, "tensors": out}
+        sd = {"world_size": self.N, "rank": self.R, "algorithm": self.cfg.algorithm,
+              "topology": self.cfg.topology, "step": self.step_no, "tensors": out}
+        if self.outer is not None:
+            sd["machines"] = self.outer["nodes"]
+            sd["between_machines"] = {
+                f"{s.entry.name}.{s.part}": {
+                    **{k: v.detach().cpu().clone() for k, v in st.items()},
+                    **{f"server_{k}": v.detach().cpu().clone() for k, v in sst.items()}}
+                for b in self.buckets if b.fused for s, (_, _, st, sst) in zip(b.segs, b.outer)}
+        return sd
 
     def load_state_dict(self, sd: dict):
         self.step_no = int(sd.get("step", 0))
@@ -551,6 +660,19 @@ class GradSyncEngine:
                     key = f"server_{k}.{i}"
                     if key in d and d[key].numel() == v.numel():
                         v.copy_(d[key])
+        saved = sd.get("between_machines")
+        if self.outer is not None and saved and sd.get("machines") == self.outer["nodes"]:
+            for b in self.buckets:
+                if not b.fused:
+                    continue
+                for s, (_, _, st, sst) in zip(b.segs, b.outer):
+                    d = saved.get(f"{s.entry.name}.{s.part}", {})
+                    for k, v in st.items():
+                        if k in d and d[k].numel() == v.numel():
+                            v.copy_(d[k])
+                    for k, v in sst.items():
+                        if f"server_{k}" in d and d[f"server_{k}"].numel() == v.numel():
+                            v.copy_(d[f"server_{k}"])
 
     def stats(self) -> dict:
         comp_elems = sum(e.numel for e in self.entries if e.compress and self.backend != "allreduce")

@@ -35,7 +35,7 @@ class FlatSyncer:
     def _state(self, key, n, device):
         st = self.state.get(key)
         if st is None or st[2] != n:
-            N = comm.size()
+            N = comm.group_size(self.group)
             sp = self.comp.spec
             s = {k: torch.zeros(n, dtype=torch.float32, device=device) for k in sp.state_names()}
             server = {}

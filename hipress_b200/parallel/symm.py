@@ -19,7 +19,7 @@ from . import comm
 class SymmetricArena:
     def __init__(self, nbytes: int, group=None):
         self.nbytes = (int(nbytes) + 4095) // 4096 * 4096
-        self.size, self.rank = comm.size(), comm.rank()
+        self.size, self.rank = comm.group_size(group), comm.group_rank(group)
         self.group = group
         L = _lib.cuda()
         p = C.c_void_p()

@@ -209,3 +209,64 @@ def test_overlapped_optimizer_step_matches_plain_step():
         assert torch.equal(a, b)
     for a, b in zip(over[0]["params"], over[1]["params"]):
         assert torch.equal(a, b)
+
+
+# ----------------------------------------------------------------------------
+def _run_two_machines(rank, world, alg, topo, per_machine, steps):
+    """`world` gloo ranks posing as world/per_machine machines."""
+    import os
+    import hipress_b200 as hp
+    os.environ["HIPRESS_NODE_ID"] = f"machine{rank // per_machine}"
+    params = [torch.nn.Parameter(torch.zeros(s)) for s in SHAPES]
+    names = ["fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
+    opt = hp.DistributedOptimizer(torch.optim.SGD(params, lr=1.0), list(zip(names, params)),
+                                  algorithm=alg, topology=topo, comp_threshold=1024,
+                                  threshold=0.01, ratio=0.05)
+    eng = opt.engine
+    outs = []
+    for step in range(steps):
+        for p, g in zip(params, _grads(rank, step)):
+            p.grad = g.clone()
+        opt.synchronize()
+        outs.append([p.grad.clone() for p in params])
+        opt._synchronized = False
+    sd = opt.state_dict()["compressor_state"]
+    return {"outs": outs, "state": sd, "backend": eng.backend, "N": eng.N, "world": eng.world,
+            "hier": eng.outer is not None and (eng.outer["nodes"], eng.outer["local"])}
+
+
+@pytest.mark.parametrize("alg,topo", [("tbq", "ring"), ("onebit", "ps"), ("graddrop", "ps")])
+def test_two_machines_of_two_ranks_synchronise_hierarchically(alg, topo):
+    world, steps = 4, 6
+    res = _spawn(_run_two_machines, world, alg, topo, 2, steps)
+    assert all(r["hier"] == (2, 2) and r["N"] == 2 and r["world"] == 4 for r in res)
+    for r in res[1:]:                                   # replicas stay identical
+        for s in range(steps):
+            for a, b in zip(r["outs"][s], res[0]["outs"][s]):
+                assert torch.equal(a, b)
+    for s in range(steps):                              # small tensors: exact mean over the job
+        want = sum(_grads(r, s)[1] for r in range(world)) / world
+        assert torch.allclose(res[0]["outs"][s][1], want, atol=1e-8)
+    if alg == "tbq":
+        # conservation: what was delivered plus what still waits in the residuals of
+        # both levels is the exact mean (ring: no owner-side state)
+        delivered = sum(res[0]["outs"][s][0] for s in range(steps)).reshape(-1)
+        exact = sum(sum(_grads(r, s)[0] for r in range(world)) / world for s in range(steps)).reshape(-1)
+        inner = sum(r["state"]["tensors"]["fc1.weight"]["residual"] for r in res) / world
+        n = exact.numel()
+        outer = torch.zeros(n)
+        from hipress_b200.parallel.simulate import chunk_range
+        for q, r in enumerate(res):
+            lo, hi = chunk_range(n, 2, q % 2)
+            outer[lo:hi] += r["state"]["between_machines"]["fc1.weight.0"]["residual"] / 2
+        assert torch.allclose(delivered + inner + outer, exact, atol=1e-6)
+        assert not torch.allclose(delivered, exact, atol=1e-4)      # it really was quantised
+
+
+def test_one_rank_per_machine_uses_the_host_transport():
+    res = _spawn(_run_two_machines, 2, "tbq", "ring", 1, 2)
+    assert all(r["backend"] == "host" and not r["hier"] and r["N"] == 2 for r in res)
+    plain = _spawn(_run_optimizer, 2, "tbq", "ring", 2)
+    for s in range(2):
+        for a, b in zip(res[0]["outs"][s], plain[0]["outs"][s]):
+            assert torch.equal(a, b)
