@@ -96,8 +96,20 @@ def test_launcher_builds_a_local_torchrun_command(capsys):
                  "eth0", "--dry-run"])
     out = capsys.readouterr().out
     assert rc == 0 and "--nproc-per-node=4" in out and "--comp-alg tbq" in out and "--topo Ring" in out
-    with pytest.raises(SystemExit):
-        L.main(["--numprocess", "2", "--servers", "node1:1,node2:1", "--dry-run"])
+    # the reference's own example: one GPU on each of two machines, reached over ssh
+    rc = L.main(["--numprocess", "2", "--servers", "node1:1,node2:1", "--interface", "eth0",
+                 "--comp-alg", "onebit", "--topo", "PS", "--dry-run"])
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert rc == 0 and len(lines) == 2
+    for k, (line, host) in enumerate(zip(lines, ("node1", "node2"))):
+        assert line.startswith(f"ssh -p 22222 -o StrictHostKeyChecking=no {host} ")
+        assert f"--nnodes=2 --node-rank={k} --nproc-per-node=1 --master-addr node1" in line
+        assert "NCCL_SOCKET_IFNAME=eth0" in line and "--comp-alg onebit" in line
+    for bad in (["--numprocess", "3", "--servers", "node1:1,node2:2"],
+                ["--numprocess", "4", "--servers", "node1:1,node2:1"],
+                ["--numprocess", "2", "--servers", "node1:1,node1:1"]):
+        with pytest.raises(SystemExit):
+            L.main(bad + ["--dry-run"])
 
 
 def test_engine_consumes_a_secopa_plan(tmp_path):
