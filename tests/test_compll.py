@@ -312,3 +312,26 @@ def test_decode_accumulate_for_every_format(tmp_path):
     em = generate((PSE / "SparseDecodeAccumulate.pse").read_text())
     assert "n_gradient,\n" in em.wrapper_source() and ", 1, stream)" in em.wrapper_source()
     assert ", 0, stream)" in generate((PSE / "GradDropDecode.pse").read_text()).wrapper_source()
+
+
+def test_operator_library_builds_on_first_use_and_runs_on_cpu_tensors():
+    from hipress_b200.compll import available, load_op
+    names = available()
+    assert {"TbqEncode", "TbqDecode", "OnebitEncode", "TernGradEncode", "DgcEncode",
+            "GradDropEncode", "SparseDecodeAccumulate"} <= set(names)
+    enc, dec = load_op("TbqEncode"), load_op("TbqDecode")
+    assert load_op("TbqEncode") is enc                   # cached
+    n = 1000
+    g = torch.linspace(-0.03, 0.03, n)
+    r = torch.zeros(n)
+    comp = torch.zeros(4 + (n + 3) // 4, dtype=torch.uint8)
+    enc(g, r, comp, 0.01)
+    out = torch.empty(n)
+    dec(comp, out)
+    assert torch.allclose(out + r, g, atol=1e-7)
+    levels = torch.tensor([-0.01, 0.0, 0.01])
+    assert (out.unsqueeze(1) - levels).abs().min(dim=1).values.max().item() < 1e-9
+    with pytest.raises(ValueError):
+        enc(g[::2], r, comp, 0.01)                       # not contiguous
+    with pytest.raises(KeyError):
+        load_op("NoSuchOperator")
