@@ -21,6 +21,7 @@ from .parallel.optimizer import DistributedOptimizer  # noqa: F401
 # the reference's MXNet front end calls the same wrapper DistributedTrainer
 DistributedTrainer = DistributedOptimizer
 from .parallel.engine import GradSyncEngine  # noqa: F401
-from .ops import Compressor, get_algorithm, algorithm_names  # noqa: F401
+from .ops import (Compressor, algorithm_names, get_algorithm, register_algorithm,  # noqa: F401
+                  unregister_algorithm)
 
 __version__ = "0.1.0"

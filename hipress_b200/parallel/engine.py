@@ -147,10 +147,16 @@ class GradSyncEngine:
         self.device = named[0][1].device
         self.on_cuda = self.device.type == "cuda"
         self.compress = cfg.algorithm not in ("none", None, "")
-        self.comp = Compressor(get_algorithm(cfg.algorithm, **cfg.algorithm_kwargs())) \
-            if self.compress else None
+        from ..ops.custom import custom_compressor
+        custom = custom_compressor(cfg.algorithm) if self.compress else None
+        self.comp = custom or (Compressor(get_algorithm(cfg.algorithm, **cfg.algorithm_kwargs()))
+                               if self.compress else None)
         backend = cfg.backend
-        if force_host:
+        if force_host or custom is not None:
+            # user-registered algorithms run from decoupled primitives: there is no
+            # fused kernel for an encode/decode pair the runtime has never seen
+            if custom is not None and backend == "fused":
+                raise ValueError(f"{cfg.algorithm} is a registered algorithm: it has no fused backend")
             backend = "host"
         if backend == "auto":
             backend = "fused" if self.on_cuda else "host"

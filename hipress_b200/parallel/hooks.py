@@ -27,7 +27,9 @@ class FlatSyncer:
     def __init__(self, config=None, group=None):
         self.cfg = config or HipressConfig()
         self.group = group
-        self.comp = Compressor(get_algorithm(self.cfg.algorithm, **self.cfg.algorithm_kwargs()))
+        from ..ops.custom import custom_compressor
+        self.comp = custom_compressor(self.cfg.algorithm) or \
+            Compressor(get_algorithm(self.cfg.algorithm, **self.cfg.algorithm_kwargs()))
         self.sched = None
         self.state = {}
         self.step = 0
