@@ -335,3 +335,22 @@ def test_operator_library_builds_on_first_use_and_runs_on_cpu_tensors():
         enc(g[::2], r, comp, 0.01)                       # not contiguous
     with pytest.raises(KeyError):
         load_op("NoSuchOperator")
+
+
+def test_new_algorithm_example_trains_on_two_cpu_ranks(tmp_path):
+    """The worked example: DSL source -> operators -> registered algorithm ->
+    data-parallel training, launched the way its docstring says."""
+    import json
+    import subprocess
+    from _mp import free_port
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(free_port()), "-m",
+                        "hipress_b200.compll.examples.train_with_new_algorithm", "--steps", "25",
+                        "--topo", "ps", "--out", str(tmp_path)],
+                       capture_output=True, text=True, cwd=root, timeout=600,
+                       env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads([row for row in r.stdout.splitlines() if row.startswith("{")][-1])
+    assert line["replicas_identical"] and line["backend"] == "host" and line["ranks"] == 2
+    assert line["last_loss"] < 0.2 * line["first_loss"] and line["compressed_fraction"] > 0.9
