@@ -53,6 +53,7 @@ def reform_process_group(new_rank: int, new_world: int, *, port: int, backend: s
         except Exception as e:  # pragma: no cover - best effort
             log.warning("destroy_process_group: %s", e)
     comm._state.update(init=False, own_pg=False)
+    comm._state.pop("hier", None)   # the machine layout is rediscovered for the new membership
     os.environ.update(RANK=str(new_rank), WORLD_SIZE=str(new_world), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
     if new_world > 1:
