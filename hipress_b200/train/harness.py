@@ -109,6 +109,68 @@ class Job:
             done.record(cur)
             used[i & 1] = done
 
+    # ------------------------------------------------------------ real data
+    def image_folder_loader(self, root, *, epoch: int = 0, workers: int = 4, image_size: int = 224):
+        """ImageNet-style directory (one sub-directory per class) as a sharded,
+        shuffled loader of pinned host batches: the data path of the reference's
+        ``pytorch_imagenet.py`` (``--train-dir``), with the standard training
+        augmentation.  Every rank reads a disjoint shard of each epoch."""
+        from torch.utils.data import DataLoader
+        from torch.utils.data.distributed import DistributedSampler
+        from torchvision import datasets, transforms
+        tf = transforms.Compose([
+            transforms.RandomResizedCrop(image_size), transforms.RandomHorizontalFlip(),
+            transforms.ToTensor(),
+            transforms.Normalize(mean=[0.485, 0.456, 0.406], std=[0.229, 0.224, 0.225])])
+        ds = datasets.ImageFolder(root, tf)
+        sampler = DistributedSampler(ds, num_replicas=comm.size(), rank=comm.rank(), shuffle=True,
+                                     drop_last=True)
+        sampler.set_epoch(epoch)
+        return DataLoader(ds, batch_size=self.batch, sampler=sampler, num_workers=workers,
+                          pin_memory=self.device.type == "cuda", drop_last=True)
+
+    def stream_from(self, host_batches):
+        """Device batches from any iterable of host batches (a DataLoader), with the
+        copy of batch i+1 issued on a side stream while step i computes."""
+        it = iter(host_batches)
+        if self.device.type != "cuda":
+            for hx, hy in it:
+                yield self.to_device(hx, hy)
+            return
+        first = next(it, None)
+        if first is None:
+            return
+        side = torch.cuda.Stream()
+        bufs = [(torch.empty_like(first[0], device=self.device), torch.empty_like(first[1], device=self.device))
+                for _ in range(2)]
+        used = [None, None]
+
+        def issue(i, host):
+            bx, by = bufs[i & 1]
+            if used[i & 1] is not None:
+                side.wait_event(used[i & 1])
+            with torch.cuda.stream(side):
+                bx.copy_(host[0], non_blocking=True)
+                by.copy_(host[1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(side)
+            return bx, by, ev, host   # the host batch stays referenced until its copy is waited for
+
+        i, nxt = 0, issue(0, first)
+        while nxt is not None:
+            x, y, ev, _ = nxt
+            host = next(it, None)
+            nxt = issue(i + 1, host) if host is not None else None
+            cur = torch.cuda.current_stream()
+            cur.wait_event(ev)
+            if self.kind == "image":
+                x = x.contiguous(memory_format=torch.channels_last)
+            yield x, y
+            done = torch.cuda.Event()
+            done.record(cur)
+            used[i & 1] = done
+            i += 1
+
     def h2d_bytes(self, x, y):
         return x.numel() * x.element_size() + y.numel() * y.element_size()
 

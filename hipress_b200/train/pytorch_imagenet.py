@@ -1,4 +1,5 @@
-"""PyTorch training script with synthetic data, flags as in the reference's
+"""PyTorch training script (synthetic data, or an ImageNet-style directory with
+``--train-dir``), flags as in the reference's
 ``horovod-torch/imageNet/pytorch_imagenet.py`` (``--batch-size --epochs
 --num-iterations --model --algorithm``, README.md:184-186 of mark14wu/hipress).
 
@@ -8,6 +9,7 @@
 from __future__ import annotations
 
 import argparse
+import itertools
 import sys
 import time
 
@@ -25,6 +27,11 @@ def main(argv=None):
     ap.add_argument("--batch-size", type=int, default=None, help="per-GPU batch")
     ap.add_argument("--epochs", type=int, default=1)
     ap.add_argument("--num-iterations", type=int, default=20, help="iterations per epoch")
+    ap.add_argument("--train-dir", default=None,
+                    help="image models: ImageNet-style directory instead of synthetic data")
+    ap.add_argument("--workers", type=int, default=4, help="--train-dir: loader processes per rank")
+    ap.add_argument("--image-size", type=int, default=224)
+    ap.add_argument("--num-classes", type=int, default=None)
     ap.add_argument("--seq-len", type=int, default=128)
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--fp32", action="store_true", help="no bf16 autocast")
@@ -37,7 +44,10 @@ def main(argv=None):
     log = setup_logging()
     cfg = config_from_args(a)
     job = build_job(a.model, cfg, batch=a.batch_size, seq_len=a.seq_len, lr=a.lr,
-                    dtype=torch.float32 if a.fp32 else torch.bfloat16)
+                    dtype=torch.float32 if a.fp32 else torch.bfloat16,
+                    model_kwargs={"num_classes": a.num_classes} if a.num_classes else None)
+    if a.train_dir and job.kind != "image":
+        raise SystemExit("--train-dir is for the image models")
     start_epoch = 0
     if a.resume and a.checkpoint_dir:
         info = load_checkpoint(a.checkpoint_dir, job.model, job.optimizer, map_location=job.device)
@@ -53,10 +63,16 @@ def main(argv=None):
         if cuda:
             torch.cuda.synchronize()
         t0 = time.time()
-        for it, (x, y) in enumerate(job.stream_batches(hosts, a.num_iterations)):
+        if a.train_dir:   # real data: a.num_iterations > 0 caps the epoch
+            loader = job.image_folder_loader(a.train_dir, epoch=epoch, workers=a.workers,
+                                             image_size=a.image_size)
+            batches = job.stream_from(itertools.islice(loader, a.num_iterations or None))
+        else:
+            batches = job.stream_batches(hosts, a.num_iterations)
+        for it, (x, y) in enumerate(batches):
             loss = job.step(x, y)
             step += 1
-            if it % 10 == 9 or it == a.num_iterations - 1:
+            if it % 10 == 9 or it == a.num_iterations - 1 or (a.train_dir and it == 0):
                 lv = loss.item()
                 dt = time.time() - t0
                 ips = job.batch * hp.size() * (it + 1) / dt

@@ -282,3 +282,23 @@ def test_full_size_models_have_the_published_parameter_counts():
     assert counts["vgg19"] == 143_667_240 and counts["resnet50"] == 25_557_032
     assert 334e6 < counts["bert_large"] < 337e6 and 109e6 < counts["bert_base"] < 111e6
     assert 130e6 < counts["lstm"] < 140e6 and 55e6 < counts["transformer"] < 65e6
+
+
+def test_training_script_reads_an_image_folder(tmp_path):
+    """--train-dir: ImageNet-style directory -> sharded loader -> training steps."""
+    from PIL import Image
+    import numpy as np
+    from hipress_b200.train import pytorch_imagenet as T
+    rng = np.random.default_rng(0)
+    for cls in ("cat", "dog"):
+        d = tmp_path / "train" / cls
+        d.mkdir(parents=True)
+        for i in range(3):
+            Image.fromarray(rng.integers(0, 255, (40, 48, 3), dtype=np.uint8)).save(d / f"{i}.png")
+    rc = T.main(["--model", "resnet50", "--num-classes", "2", "--batch-size", "2", "--image-size", "32",
+                 "--train-dir", str(tmp_path / "train"), "--workers", "0", "--num-iterations", "2",
+                 "--fp32", "--algorithm", "tbq", "--comp-threshold", "100000",
+                 "--metrics", str(tmp_path / "m.jsonl")])
+    assert rc == 0
+    recs = [json.loads(r) for r in (tmp_path / "m.jsonl").read_text().splitlines()]
+    assert recs and recs[-1]["step"] == 2 and recs[-1]["loss"] == recs[-1]["loss"]
