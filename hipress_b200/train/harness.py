@@ -110,7 +110,8 @@ class Job:
             used[i & 1] = done
 
     # ------------------------------------------------------------ real data
-    def image_folder_loader(self, root, *, epoch: int = 0, workers: int = 4, image_size: int = 224):
+    def image_folder_loader(self, root, *, epoch: int = 0, workers: int = 4, image_size: int = 224,
+                            train: bool = True):
         """ImageNet-style directory (one sub-directory per class) as a sharded,
         shuffled loader of pinned host batches: the data path of the reference's
         ``pytorch_imagenet.py`` (``--train-dir``), with the standard training
@@ -118,16 +119,38 @@ class Job:
         from torch.utils.data import DataLoader
         from torch.utils.data.distributed import DistributedSampler
         from torchvision import datasets, transforms
-        tf = transforms.Compose([
-            transforms.RandomResizedCrop(image_size), transforms.RandomHorizontalFlip(),
-            transforms.ToTensor(),
-            transforms.Normalize(mean=[0.485, 0.456, 0.406], std=[0.229, 0.224, 0.225])])
+        norm = transforms.Normalize(mean=[0.485, 0.456, 0.406], std=[0.229, 0.224, 0.225])
+        if train:
+            tf = transforms.Compose([transforms.RandomResizedCrop(image_size),
+                                     transforms.RandomHorizontalFlip(), transforms.ToTensor(), norm])
+        else:   # validation: resize the short side, centre crop, no shuffling, no dropped images
+            tf = transforms.Compose([transforms.Resize(image_size * 8 // 7), transforms.CenterCrop(image_size),
+                                     transforms.ToTensor(), norm])
         ds = datasets.ImageFolder(root, tf)
-        sampler = DistributedSampler(ds, num_replicas=comm.size(), rank=comm.rank(), shuffle=True,
-                                     drop_last=True)
+        sampler = DistributedSampler(ds, num_replicas=comm.size(), rank=comm.rank(), shuffle=train,
+                                     drop_last=train)
         sampler.set_epoch(epoch)
         return DataLoader(ds, batch_size=self.batch, sampler=sampler, num_workers=workers,
-                          pin_memory=self.device.type == "cuda", drop_last=True)
+                          pin_memory=self.device.type == "cuda", drop_last=train)
+
+    @torch.no_grad()
+    def evaluate(self, loader):
+        """Top-1 accuracy and mean loss of an image model over `loader`, summed over
+        all ranks (each rank scores its own shard)."""
+        was = self.model.training
+        self.model.eval()
+        tot = torch.zeros(3, dtype=torch.float64, device=self.device)   # correct, loss sum, count
+        for hx, hy in loader:
+            x, y = self.to_device(hx, hy)
+            with torch.autocast(self.device.type, dtype=self.dtype, enabled=self.dtype != torch.float32):
+                out = self.model(x).float()
+            tot[0] += (out.argmax(1) == y).sum()
+            tot[1] += F.cross_entropy(out, y, reduction="sum")
+            tot[2] += y.numel()
+        comm.allreduce_(tot, average=False)
+        self.model.train(was)
+        n = max(tot[2].item(), 1.0)
+        return {"top1": tot[0].item() / n, "loss": tot[1].item() / n, "images": int(tot[2].item())}
 
     def stream_from(self, host_batches):
         """Device batches from any iterable of host batches (a DataLoader), with the

@@ -29,7 +29,10 @@ def main(argv=None):
     ap.add_argument("--num-iterations", type=int, default=20, help="iterations per epoch")
     ap.add_argument("--train-dir", default=None,
                     help="image models: ImageNet-style directory instead of synthetic data")
+    ap.add_argument("--val-dir", default=None, help="image models: directory scored after every epoch")
     ap.add_argument("--workers", type=int, default=4, help="--train-dir: loader processes per rank")
+    ap.add_argument("--warmup-iters", type=int, default=0, help="linear learning-rate warm-up")
+    ap.add_argument("--lr-decay-epochs", default="", help="e.g. 30,60,80: multiply the rate by 0.1 there")
     ap.add_argument("--image-size", type=int, default=224)
     ap.add_argument("--num-classes", type=int, default=None)
     ap.add_argument("--seq-len", type=int, default=128)
@@ -59,6 +62,16 @@ def main(argv=None):
     cuda = job.device.type == "cuda"
     hosts = [job.host_batch(100 * hp.rank() + i) for i in range(4)]
     step = 0
+    base_lrs = [g["lr"] for g in job.optimizer.param_groups]
+    decay_at = [int(e) for e in a.lr_decay_epochs.split(",") if e.strip()]
+
+    def set_lr(epoch, step):
+        scale = 0.1 ** sum(epoch >= e for e in decay_at)
+        if a.warmup_iters and step < a.warmup_iters:
+            scale *= (step + 1) / a.warmup_iters
+        for g, base in zip(job.optimizer.param_groups, base_lrs):
+            g["lr"] = base * scale
+
     for epoch in range(start_epoch, a.epochs):
         if cuda:
             torch.cuda.synchronize()
@@ -70,6 +83,7 @@ def main(argv=None):
         else:
             batches = job.stream_batches(hosts, a.num_iterations)
         for it, (x, y) in enumerate(batches):
+            set_lr(epoch, step)
             loss = job.step(x, y)
             step += 1
             if it % 10 == 9 or it == a.num_iterations - 1 or (a.train_dir and it == 0):
@@ -79,6 +93,13 @@ def main(argv=None):
                 log.info("epoch %d iter %d loss %.4f  %.1f samples/s", epoch, it + 1, lv, ips)
                 mw.step(step, epoch=epoch, loss=lv, samples_per_s=round(ips, 1),
                         **engine_metrics(job.optimizer.engine))
+        if a.val_dir:
+            score = job.evaluate(job.image_folder_loader(a.val_dir, workers=a.workers,
+                                                         image_size=a.image_size, train=False))
+            log.info("epoch %d validation: top-1 %.4f, loss %.4f over %d images", epoch,
+                     score["top1"], score["loss"], score["images"])
+            mw.step(step, epoch=epoch, val_top1=round(score["top1"], 5), val_loss=round(score["loss"], 5),
+                    val_images=score["images"])
         if a.checkpoint_dir:
             save_checkpoint(a.checkpoint_dir, job.model, job.optimizer, epoch=epoch + 1, step=step)
     job.optimizer.engine.check() if cuda else None

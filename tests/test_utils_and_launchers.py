@@ -296,9 +296,13 @@ def test_training_script_reads_an_image_folder(tmp_path):
         for i in range(3):
             Image.fromarray(rng.integers(0, 255, (40, 48, 3), dtype=np.uint8)).save(d / f"{i}.png")
     rc = T.main(["--model", "resnet50", "--num-classes", "2", "--batch-size", "2", "--image-size", "32",
-                 "--train-dir", str(tmp_path / "train"), "--workers", "0", "--num-iterations", "2",
+                 "--train-dir", str(tmp_path / "train"), "--val-dir", str(tmp_path / "train"),
+                 "--workers", "0", "--num-iterations", "2", "--warmup-iters", "2", "--lr-decay-epochs", "1",
                  "--fp32", "--algorithm", "tbq", "--comp-threshold", "100000",
                  "--metrics", str(tmp_path / "m.jsonl")])
     assert rc == 0
     recs = [json.loads(r) for r in (tmp_path / "m.jsonl").read_text().splitlines()]
-    assert recs and recs[-1]["step"] == 2 and recs[-1]["loss"] == recs[-1]["loss"]
+    train = [r for r in recs if "loss" in r]
+    assert train and train[-1]["step"] == 2 and train[-1]["loss"] == train[-1]["loss"]
+    val = [r for r in recs if "val_top1" in r]
+    assert val and val[-1]["val_images"] == 6 and 0.0 <= val[-1]["val_top1"] <= 1.0
