@@ -79,6 +79,22 @@ class DistributedOptimizer:
         self.engine.synchronize()
         self._synchronized = True
 
+    def skip_synchronize(self):
+        """Horovod's context manager for ``synchronize(); clip; with
+        skip_synchronize(): step()``.  ``step()`` already skips a second
+        synchronisation after an explicit ``synchronize()``, so this only marks the
+        gradients as synchronised for the duration of the block."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def ctx():
+            before, self._synchronized = self._synchronized, True
+            try:
+                yield
+            finally:
+                self._synchronized = before if self._synchronized else False
+        return ctx()
+
     def step(self, closure=None):
         if not self._synchronized:
             self.engine.synchronize()

@@ -96,3 +96,15 @@ def test_plan_auto_uses_a_measured_profile(tmp_path):
     # no profile for this world size: the threshold decides
     eng = _engine([4_000_000, 1_000_000, 100], algorithm="tbq", plan="auto", comp_threshold=500_000)
     assert [e.compress for e in eng.entries] == [True, True, False]
+
+
+def test_horovod_clipping_pattern_with_skip_synchronize():
+    p = torch.nn.Parameter(torch.zeros(4))
+    opt = hp.DistributedOptimizer(torch.optim.SGD([p], lr=1.0), [("w", p)], algorithm="none")
+    p.grad = torch.full((4,), 3.0)
+    opt.synchronize()
+    torch.nn.utils.clip_grad_norm_([p], 1.0)
+    with opt.skip_synchronize():
+        opt.step()
+    assert torch.allclose(p.detach(), torch.full((4,), -0.5)) and not opt._synchronized
+    opt.close()
