@@ -321,3 +321,11 @@ def test_builtin_names_cannot_be_registered():
     import hipress_b200 as hp
     with pytest.raises(ValueError):
         hp.register_algorithm("tbq", encode=None, decode=None, payload_bytes=None)
+
+
+def test_machines_of_different_sizes_fall_back_to_the_host_transport():
+    res = _spawn(_run_two_machines, 3, "tbq", "ring", 2, 2)      # machines of 2 and 1 ranks
+    assert all(r["backend"] == "host" and not r["hier"] and r["N"] == 3 for r in res)
+    for s in range(2):
+        for a, b in zip(res[0]["outs"][s], res[2]["outs"][s]):
+            assert torch.equal(a, b)
