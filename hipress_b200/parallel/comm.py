@@ -94,8 +94,9 @@ def hierarchy():
       group of the ranks with its local index on every machine (only for equal
       machine sizes above 1).
 
-    Machines are told apart by host name; ``HIPRESS_NODE_ID`` overrides it (one
-    machine can then stand in for several).  Collective over the job: every rank
+    Machines are told apart by host name; ``HIPRESS_NODE_ID`` (per rank) or
+    ``HIPRESS_NODE_SIZE=K`` (consecutive ranks in groups of K) override it, so one
+    machine can stand in for several.  Collective over the job: every rank
     must call it at the same point.  The result is cached."""
     if "hier" in _state:
         return _state["hier"]
@@ -103,6 +104,8 @@ def hierarchy():
     if size() > 1:
         import socket
         ident = os.environ.get("HIPRESS_NODE_ID") or socket.gethostname()
+        if os.environ.get("HIPRESS_NODE_SIZE"):   # consecutive ranks in groups of K pose as machines
+            ident = f"node{rank() // max(1, int(os.environ['HIPRESS_NODE_SIZE']))}"
         ids = [None] * size()
         dist.all_gather_object(ids, ident)
         order = list(dict.fromkeys(ids))

@@ -216,7 +216,10 @@ def _run_two_machines(rank, world, alg, topo, per_machine, steps):
     """`world` gloo ranks posing as world/per_machine machines."""
     import os
     import hipress_b200 as hp
-    os.environ["HIPRESS_NODE_ID"] = f"machine{rank // per_machine}"
+    if per_machine == 2 and world == 4:
+        os.environ["HIPRESS_NODE_SIZE"] = "2"                 # the job-wide spelling
+    else:
+        os.environ["HIPRESS_NODE_ID"] = f"machine{rank // per_machine}"
     params = [torch.nn.Parameter(torch.zeros(s)) for s in SHAPES]
     names = ["fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
     opt = hp.DistributedOptimizer(torch.optim.SGD(params, lr=1.0), list(zip(names, params)),
