@@ -41,6 +41,8 @@ def main(argv=None):
     ap.add_argument("--checkpoint-dir", default=None)
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--metrics", default=None, help="JSONL file for per-step metrics")
+    ap.add_argument("--heartbeat-timeout", type=float, default=0.0,
+                    help="seconds without a peer's heartbeat before the job stops (0: no monitor)")
     add_hipress_args(ap)
     a = ap.parse_args(argv)
     hp.init()
@@ -61,6 +63,10 @@ def main(argv=None):
              engine_metrics(job.optimizer.engine))
     cuda = job.device.type == "cuda"
     hosts = [job.host_batch(100 * hp.rank() + i) for i in range(4)]
+    monitor = None
+    if a.heartbeat_timeout > 0 and hp.size() > 1:
+        from hipress_b200.utils.health import HealthMonitor, default_store
+        monitor = HealthMonitor(default_store(), hp.rank(), hp.size(), timeout_s=a.heartbeat_timeout)
     step = 0
     base_lrs = [g["lr"] for g in job.optimizer.param_groups]
     decay_at = [int(e) for e in a.lr_decay_epochs.split(",") if e.strip()]
@@ -84,6 +90,10 @@ def main(argv=None):
             batches = job.stream_batches(hosts, a.num_iterations)
         for it, (x, y) in enumerate(batches):
             set_lr(epoch, step)
+            if monitor is not None:
+                # between steps, nothing of this rank in flight: a peer that left or went
+                # silent ends the job here instead of inside the next collective
+                monitor.check()
             loss = job.step(x, y)
             step += 1
             if it % 10 == 9 or it == a.num_iterations - 1 or (a.train_dir and it == 0):
@@ -103,6 +113,8 @@ def main(argv=None):
         if a.checkpoint_dir:
             save_checkpoint(a.checkpoint_dir, job.model, job.optimizer, epoch=epoch + 1, step=step)
     job.optimizer.engine.check() if cuda else None
+    if monitor is not None:
+        monitor.leave()
     mw.close()
     job.optimizer.close()
     hp.shutdown()
