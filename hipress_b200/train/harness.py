@@ -194,6 +194,21 @@ class Job:
             used[i & 1] = done
             i += 1
 
+    def rebuild_optimizer(self):
+        """After the process group was re-formed with another membership: a new
+        DistributedOptimizer (buckets, arenas, hooks) around the same model and inner
+        optimizer.  Compressor state is rank-local error memory of the old
+        membership and starts from zero; parameters and optimizer state are taken
+        from the new rank 0 so the replicas agree again."""
+        old = self.optimizer
+        inner, cfg = old.optimizer, old.config
+        old.close()
+        named = list(self.model.gluon_named_parameters()) if hasattr(self.model, "gluon_named_parameters") \
+            else list(self.model.named_parameters())
+        self.optimizer = DistributedOptimizer(inner, named, cfg)
+        broadcast_parameters(self.model.state_dict(), root_rank=0)
+        comm.broadcast_optimizer_state(inner, root_rank=0)
+
     def h2d_bytes(self, x, y):
         return x.numel() * x.element_size() + y.numel() * y.element_size()
 

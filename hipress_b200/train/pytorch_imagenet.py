@@ -43,6 +43,13 @@ def main(argv=None):
     ap.add_argument("--metrics", default=None, help="JSONL file for per-step metrics")
     ap.add_argument("--heartbeat-timeout", type=float, default=0.0,
                     help="seconds without a peer's heartbeat before the job stops (0: no monitor)")
+    ap.add_argument("--elastic", action="store_true",
+                    help="with --heartbeat-timeout: when peers leave or go silent, the survivors "
+                         "re-form a smaller job and continue")
+    ap.add_argument("--elastic-port", type=int, default=0,
+                    help="first rendezvous port of re-formed jobs (default MASTER_PORT + 1)")
+    ap.add_argument("--inject-leave", default=None, metavar="RANK:STEP",
+                    help="fault injection on the host: this rank leaves the job before that step")
     add_hipress_args(ap)
     a = ap.parse_args(argv)
     hp.init()
@@ -63,10 +70,17 @@ def main(argv=None):
              engine_metrics(job.optimizer.engine))
     cuda = job.device.type == "cuda"
     hosts = [job.host_batch(100 * hp.rank() + i) for i in range(4)]
-    monitor = None
-    if a.heartbeat_timeout > 0 and hp.size() > 1:
-        from hipress_b200.utils.health import HealthMonitor, default_store
-        monitor = HealthMonitor(default_store(), hp.rank(), hp.size(), timeout_s=a.heartbeat_timeout)
+    from hipress_b200.utils.health import HealthMonitor, PeerFailure, default_store
+
+    def new_monitor():
+        if a.heartbeat_timeout > 0 and hp.size() > 1:
+            return HealthMonitor(default_store(), hp.rank(), hp.size(), timeout_s=a.heartbeat_timeout,
+                                 interval_s=min(0.2, a.heartbeat_timeout / 4))
+        return None
+
+    monitor = new_monitor()
+    leave_rank, leave_step = (int(v) for v in a.inject_leave.split(":")) if a.inject_leave else (-1, -1)
+    generation = 0
     step = 0
     base_lrs = [g["lr"] for g in job.optimizer.param_groups]
     decay_at = [int(e) for e in a.lr_decay_epochs.split(",") if e.strip()]
@@ -90,10 +104,40 @@ def main(argv=None):
             batches = job.stream_batches(hosts, a.num_iterations)
         for it, (x, y) in enumerate(batches):
             set_lr(epoch, step)
+            if hp.rank() == leave_rank and step == leave_step and generation == 0:
+                log.warning("leaving the job before step %d (injected)", step)
+                if cuda:
+                    torch.cuda.synchronize()
+                if monitor is not None:
+                    monitor.leave()
+                time.sleep(max(1.0, 2 * a.heartbeat_timeout))   # stay reachable while the others regroup
+                return 0
             if monitor is not None:
                 # between steps, nothing of this rank in flight: a peer that left or went
-                # silent ends the job here instead of inside the next collective
-                monitor.check()
+                # silent is noticed here instead of inside the next collective
+                try:
+                    if step == leave_step and generation == 0 and leave_rank >= 0:
+                        time.sleep(min(1.0, a.heartbeat_timeout))   # let the injected exit be announced
+                    monitor.check()
+                except PeerFailure as e:
+                    if not a.elastic:
+                        raise SystemExit(f"rank {hp.rank()}: {e}; stopping (no --elastic)")
+                    from hipress_b200.parallel.elastic import reform_process_group, survivors_rendezvous
+                    import os
+                    generation += 1
+                    log.warning("%s: re-forming the job without them", e)
+                    if cuda:
+                        torch.cuda.synchronize()
+                    store, old_rank, old_world = default_store(), hp.rank(), hp.size()
+                    monitor.close()
+                    new_rank, new_world = survivors_rendezvous(store, old_rank, old_world, e.ranks,
+                                                               generation=generation)
+                    port = (a.elastic_port or int(os.environ.get("MASTER_PORT", "29500")) + 1) + generation - 1
+                    reform_process_group(new_rank, new_world, port=port)
+                    job.rebuild_optimizer()
+                    monitor = new_monitor()
+                    base_lrs = [g["lr"] for g in job.optimizer.param_groups]
+                    log.warning("continuing as rank %d of %d", new_rank, new_world)
             loss = job.step(x, y)
             step += 1
             if it % 10 == 9 or it == a.num_iterations - 1 or (a.train_dir and it == 0):
@@ -101,7 +145,7 @@ def main(argv=None):
                 dt = time.time() - t0
                 ips = job.batch * hp.size() * (it + 1) / dt
                 log.info("epoch %d iter %d loss %.4f  %.1f samples/s", epoch, it + 1, lv, ips)
-                mw.step(step, epoch=epoch, loss=lv, samples_per_s=round(ips, 1),
+                mw.step(step, epoch=epoch, loss=lv, samples_per_s=round(ips, 1), ranks=hp.size(),
                         **engine_metrics(job.optimizer.engine))
         if a.val_dir:
             score = job.evaluate(job.image_folder_loader(a.val_dir, workers=a.workers,

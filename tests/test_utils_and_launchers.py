@@ -306,3 +306,23 @@ def test_training_script_reads_an_image_folder(tmp_path):
     assert train and train[-1]["step"] == 2 and train[-1]["loss"] == train[-1]["loss"]
     val = [r for r in recs if "val_top1" in r]
     assert val and val[-1]["val_images"] == 6 and 0.0 <= val[-1]["val_top1"] <= 1.0
+
+
+def _elastic_training_worker(rank, world, port2, outdir):
+    from hipress_b200.train import pytorch_imagenet as T
+    rc = T.main(["--model", "bert_tiny", "--batch-size", "2", "--seq-len", "16", "--num-iterations", "6",
+                 "--fp32", "--algorithm", "tbq", "--comp-threshold", "1000", "--threshold", "0.0001",
+                 "--heartbeat-timeout", "1.0", "--elastic", "--elastic-port", str(port2),
+                 "--inject-leave", "2:3", "--metrics", f"{outdir}/m{rank}.jsonl"])
+    return rc
+
+
+def test_training_script_continues_after_a_rank_leaves(tmp_path):
+    """Three ranks train; rank 2 leaves before step 3 (injected on the host); the
+    other two notice between steps, re-form a job of two and finish the epoch."""
+    from _mp import free_port
+    res = spawn(_elastic_training_worker, 3, free_port(), str(tmp_path))
+    assert res == [0, 0, 0]
+    recs = [json.loads(r) for r in (tmp_path / "m0.jsonl").read_text().splitlines()]
+    assert recs[-1]["step"] == 6 and recs[-1]["ranks"] == 2
+    assert recs[-1]["loss"] == recs[-1]["loss"]
