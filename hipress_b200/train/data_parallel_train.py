@@ -12,7 +12,9 @@ per GPU) with ``torch.distributed.run``.  A list with other machines
 22222 in the reference's setup, README.md:29-39), with the first host as the
 rendezvous address; ``--interface`` selects the network interface of NCCL and
 gloo, as in the reference.  ``--horovodrun`` is accepted for command-line
-compatibility and has no effect.
+compatibility and has no effect.  Flags the launcher does not know
+(``--train-dir``, ``--checkpoint-dir``, ``--elastic`` ...) are handed to the
+training script.
 """
 from __future__ import annotations
 
@@ -41,7 +43,7 @@ def _train_args(a) -> list[str]:
         args += ["--batch-size", str(a.batch_size)]
     if a.comprplan:
         args += ["--comprplan", a.comprplan]
-    return args
+    return args + list(getattr(a, "extra", []))   # anything else goes to the training script
 
 
 def _is_local(host: str) -> bool:
@@ -111,7 +113,7 @@ def main(argv=None):
     ap.add_argument("--epochs", type=int, default=1)
     ap.add_argument("--port", type=int, default=29500)
     ap.add_argument("--dry-run", action="store_true", help="print the command and exit")
-    a = ap.parse_args(argv)
+    a, a.extra = ap.parse_known_args(argv)
     cmds = build_commands(a)
     if a.dry_run:
         for _, cmd in cmds:
