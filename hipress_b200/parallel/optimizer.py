@@ -122,6 +122,10 @@ class DistributedOptimizer:
                 self.engine.load_state_dict(sd["compressor_state"])
         else:
             self.optimizer.load_state_dict(sd)
+        if self._bucket_opts is not None:
+            # loading replaces the wrapped optimizer's state mapping: share the new one
+            for bo, _ in self._bucket_opts.values():
+                bo.state = self.optimizer.state
 
     def close(self):
         self.engine.close()

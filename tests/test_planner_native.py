@@ -108,3 +108,42 @@ def test_horovod_clipping_pattern_with_skip_synchronize():
         opt.step()
     assert torch.allclose(p.detach(), torch.full((4,), -0.5)) and not opt._synchronized
     opt.close()
+
+
+def test_overlapped_optimizer_keeps_sharing_state_after_a_checkpoint_load():
+    def make(overlap):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Linear(64, 8))
+        inner = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+        opt = hp.DistributedOptimizer(inner, list(model.named_parameters()), algorithm="tbq",
+                                      comp_threshold=1000, threshold=1e-4, bucket_bytes=4096,
+                                      overlap_optimizer=overlap)
+        return model, opt
+
+    def run(model, opt, steps, seed):
+        g = torch.Generator().manual_seed(seed)
+        for _ in range(steps):
+            opt.zero_grad()
+            model(torch.randn(8, 32, generator=g)).square().mean().backward()
+            opt.step()
+
+    ref_m, ref_o = make(False)
+    run(ref_m, ref_o, 4, 1)
+    m1, o1 = make(True)
+    run(m1, o1, 2, 1)
+    sd = {"model": {k: v.clone() for k, v in m1.state_dict().items()}, "opt": o1.state_dict()}
+    m2, o2 = make(True)                      # a fresh job resumes from the checkpoint
+    m2.load_state_dict(sd["model"])
+    o2.load_state_dict(sd["opt"])
+    g = torch.Generator().manual_seed(1)
+    for _ in range(2):
+        torch.randn(8, 32, generator=g)      # skip the batches the first job consumed
+    for _ in range(2):
+        o2.zero_grad()
+        m2(torch.randn(8, 32, generator=g)).square().mean().backward()
+        o2.step()
+    for a, b in zip(ref_m.parameters(), m2.parameters()):
+        assert torch.allclose(a, b, atol=1e-7)
+    assert len(o2.optimizer.state_dict()["state"]) == 4
+    for o in (ref_o, o1, o2):
+        o.close()
