@@ -157,6 +157,8 @@ def broadcast_optimizer_state(optimizer, root_rank: int = 0):
     dist.broadcast_object_list(obj, src=root_rank)
     if rank() != root_rank:
         opt.load_state_dict(obj[0])
+        if hasattr(optimizer, "_relink"):
+            optimizer._relink()
 
 
 _syncers: dict = {}

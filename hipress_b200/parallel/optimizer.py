@@ -122,8 +122,12 @@ class DistributedOptimizer:
                 self.engine.load_state_dict(sd["compressor_state"])
         else:
             self.optimizer.load_state_dict(sd)
+        self._relink()
+
+    def _relink(self):
+        """Loading a state dict replaces the wrapped optimizer's state mapping: the
+        per-bucket optimizers of the overlapped step must share the new one."""
         if self._bucket_opts is not None:
-            # loading replaces the wrapped optimizer's state mapping: share the new one
             for bo, _ in self._bucket_opts.values():
                 bo.state = self.optimizer.state
 
