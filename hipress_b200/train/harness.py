@@ -207,7 +207,7 @@ class Job:
             else list(self.model.named_parameters())
         self.optimizer = DistributedOptimizer(inner, named, cfg)
         broadcast_parameters(self.model.state_dict(), root_rank=0)
-        comm.broadcast_optimizer_state(inner, root_rank=0)
+        comm.broadcast_optimizer_state(self.optimizer, root_rank=0)
 
     def h2d_bytes(self, x, y):
         return x.numel() * x.element_size() + y.numel() * y.element_size()
