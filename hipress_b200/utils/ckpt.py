@@ -29,8 +29,8 @@ def save_checkpoint(directory, model, optimizer, *, epoch=0, step=0, extra=None)
     if comm.rank() == 0:
         tmp = d / "model.pt.tmp"
         torch.save({"model": model.state_dict(), "optimizer": inner.state_dict(), "epoch": epoch,
-                    "step": step, "config": vars(getattr(optimizer, "config", None) or object())
-                    if hasattr(optimizer, "config") else {}, "extra": extra}, tmp)
+                    "step": step, "config": dict(vars(optimizer.config)) if hasattr(optimizer, "config")
+                    else {}, "extra": extra}, tmp)
         os.replace(tmp, d / "model.pt")
     if hasattr(optimizer, "engine"):
         tmp = d / f"rank{comm.rank()}.pt.tmp"
@@ -47,6 +47,8 @@ def load_checkpoint(directory, model, optimizer, map_location=None) -> dict:
     model.load_state_dict(ck["model"])
     inner = getattr(optimizer, "optimizer", optimizer)
     inner.load_state_dict(ck["optimizer"])
+    if hasattr(optimizer, "_relink"):
+        optimizer._relink()
     mine = d / f"rank{comm.rank()}.pt"
     if hasattr(optimizer, "engine"):
         if mine.exists():
