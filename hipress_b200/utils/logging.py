@@ -12,6 +12,8 @@ import logging
 import os
 import time
 
+import torch
+
 from ..parallel import comm
 
 
@@ -59,11 +61,9 @@ def engine_metrics(engine) -> dict:
                 comp += engine.comp.payload_bytes(e.numel)
             else:
                 comp += 4 * e.numel
-    norm = 0.0
-    for e in engine.entries:
-        for k, v in e.state.items():
-            if k in ("residual", "accum_v"):
-                norm += float(v.float().pow(2).sum())
+    held = [v for e in engine.entries for k, v in e.state.items() if k in ("residual", "accum_v")]
+    # one reduction and one read of the device, whatever the number of tensors
+    norm = float(torch.linalg.vector_norm(torch.stack(torch._foreach_norm(held)))) if held else 0.0
     return {"gradient_bytes": raw, "payload_bytes": comp,
-            "compression_ratio": round(raw / max(comp, 1), 2), "residual_norm": norm ** 0.5,
+            "compression_ratio": round(raw / max(comp, 1), 2), "residual_norm": norm,
             "buckets": len(engine.buckets), "backend": engine.backend}
