@@ -11,6 +11,9 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description="SeCoPa: selective compression and partitioning",
                                  formatter_class=argparse.ArgumentDefaultsHelpFormatter)
     ap.add_argument("--input", default="input.txt", help="rows of name,size")
+    ap.add_argument("--model", default=None,
+                    help="take the gradient list from a model of the zoo (vgg19, resnet50, bert_large, "
+                         "...) instead of --input")
     ap.add_argument("--output", default="SeCoPaPlan.txt", help="rows of name,size,y|n,K")
     ap.add_argument("--topology", default="PS", choices=["PS", "RING"])
     ap.add_argument("--nnodes", type=int, default=16, help="cluster size")
@@ -27,10 +30,18 @@ def main(argv=None):
             prof = CostProfile.from_json(f.read())
         if prof.nodes != a.nnodes:
             raise SystemExit(f"profile was measured for {prof.nodes} nodes, not {a.nnodes}")
-    if a.bucketed:
-        rows = Planner(prof).plan_bucketed(read_gradient_list(a.input), a.topology, a.bucket_mb << 20)
+    if a.model:
+        from ..models import get_model
+        from .planner import gradient_list_of
+        m = get_model(a.model)
+        named = m.gluon_named_parameters() if hasattr(m, "gluon_named_parameters") else m.named_parameters()
+        grads = gradient_list_of((n, p) for n, p in named if p.requires_grad)
     else:
-        rows = Planner(prof).plan(read_gradient_list(a.input), a.topology)
+        grads = read_gradient_list(a.input)
+    if a.bucketed:
+        rows = Planner(prof).plan_bucketed(grads, a.topology, a.bucket_mb << 20)
+    else:
+        rows = Planner(prof).plan(grads, a.topology)
     with open(a.output, "w") as f:
         f.write(format_plan(rows))
 

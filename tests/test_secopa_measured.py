@@ -153,3 +153,11 @@ def test_engine_plan_auto_bucketed(tmp_path):
     # one by one, a 5000-element gradient never repays the fused launch
     assert [e.compress for e in opt.engine.entries][2:] == [False, False]
     opt.close()
+
+
+def test_cli_takes_the_gradient_list_from_the_model_zoo(tmp_path):
+    out = tmp_path / "plan.txt"
+    subprocess.run([sys.executable, "-m", "hipress_b200.secopa", "--model", "vgg19", "--output", str(out),
+                    "--topology", "PS", "--nnodes", "4"], check=True, cwd=ROOT)
+    rows = [r.split(",") for r in out.read_text().splitlines()]
+    assert len(rows) == 38 and rows[32][:2] == ["vgg0_dense0_weight", "102760448"] and rows[32][2] == "y"
