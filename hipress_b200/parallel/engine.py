@@ -144,6 +144,15 @@ class GradSyncEngine:
         named = [(n, p) for n, p in named_parameters if p.requires_grad]
         if not named:
             raise ValueError("no trainable parameters")
+        seen_names, seen_params = set(), set()
+        for n, p in named:
+            if n in seen_names:
+                raise ValueError(f"parameter name {n!r} appears twice: names key plans, state and "
+                                 "checkpoints and must be unique")
+            if id(p) in seen_params:
+                raise ValueError(f"parameter {n!r} was passed twice (a shared tensor is listed once)")
+            seen_names.add(n)
+            seen_params.add(id(p))
         self.device = named[0][1].device
         self.on_cuda = self.device.type == "cuda"
         self.compress = cfg.algorithm not in ("none", None, "")
@@ -394,6 +403,9 @@ class GradSyncEngine:
         if p.grad is None:
             p.grad = torch.zeros_like(p, memory_format=torch.preserve_format)
         g = p.grad
+        if g.is_sparse:
+            raise TypeError(f"gradient of {e.name} is a sparse tensor; use dense gradients "
+                            "(e.g. nn.Embedding(sparse=False))")
         if g.dtype != torch.float32:
             raise TypeError(f"gradient of {e.name} is {g.dtype}; fp32 gradients are required")
         if not (g.is_contiguous() or g.is_contiguous(memory_format=torch.channels_last)):

@@ -1,4 +1,5 @@
 """The native bucket planner (csrc/cpu/planner.cpp) through the engine."""
+import pytest
 import torch
 
 import hipress_b200 as hp
@@ -147,3 +148,18 @@ def test_overlapped_optimizer_keeps_sharing_state_after_a_checkpoint_load():
     assert len(o2.optimizer.state_dict()["state"]) == 4
     for o in (ref_o, o1, o2):
         o.close()
+
+
+def test_bad_parameter_lists_and_sparse_gradients_are_refused():
+    a, b = torch.nn.Parameter(torch.zeros(10)), torch.nn.Parameter(torch.zeros(10))
+    with pytest.raises(ValueError, match="twice"):
+        hp.GradSyncEngine([("w", a), ("w", b)], hp.HipressConfig(algorithm="tbq"))
+    with pytest.raises(ValueError, match="twice"):
+        hp.GradSyncEngine([("w", a), ("v", a)], hp.HipressConfig(algorithm="tbq"))
+    emb = torch.nn.Embedding(50, 40, sparse=True)
+    opt = hp.DistributedOptimizer(torch.optim.SGD(emb.parameters(), lr=0.1), list(emb.named_parameters()),
+                                  algorithm="tbq", comp_threshold=100)
+    with pytest.raises(TypeError, match="sparse"):   # raised from the hook that launches the bucket
+        emb(torch.tensor([1, 2])).sum().backward()
+        opt.step()
+    opt.close()
