@@ -12,6 +12,12 @@ N GPUs of one box, device-timed, max over ranks.
     python bench.py --sync-backend host        # unfused compressed baseline (BL1)
     python bench.py --impl reference        # the reference itself (not installable offline)
 
+After the product arm the same process times two baselines with the same model,
+batch, warm-up and steps: torch DistributedDataParallel over NCCL (the conventional
+uncompressed path the reference measures itself against, README.md:153 of
+mark14wu/hipress) and this repo's unfused compressed schedule.  Their numbers, a
+replica checksum and a one-step conservation check travel in the same JSON line.
+
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
@@ -44,7 +50,10 @@ def parse():
     ap.add_argument("--comp-alg", default=None)
     ap.add_argument("--topo", default=None)
     ap.add_argument("--comp-threshold", type=int, default=262144)
-    ap.add_argument("--comprplan", default=None)
+    ap.add_argument("--comprplan", default="auto:bucketed",
+                    help="SeCoPa plan: a plan file, 'auto' / 'auto:bucketed' (planner run in process with "
+                         "the measured B200 cost profile of this world size; the size threshold decides "
+                         "when there is none), or 'threshold'")
     ap.add_argument("--sync-backend", default="auto", choices=["auto", "fused", "host", "allreduce"])
     ap.add_argument("--ctas", type=int, default=None)
     ap.add_argument("--bucket-mb", type=int, default=None)
@@ -53,6 +62,9 @@ def parse():
     ap.add_argument("--overlap-optimizer", type=int, default=None, choices=[0, 1],
                     help="update each bucket's parameters right behind its synchronisation")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-baselines", action="store_true",
+                    help="skip the torch-DDP and unfused arms that follow the product arm")
+    ap.add_argument("--no-check", action="store_true", help="skip the one-step conservation check")
     return ap.parse_args()
 
 
@@ -111,6 +123,59 @@ def physical_index(local: int) -> int:
     return local
 
 
+def timed_steps(job, pool, steps, warmup, sync_all, N, dev):
+    """`warmup` untimed steps, then `steps` steps between two CUDA events (barrier +
+    synchronize on both sides).  Returns (ms total, max over ranks; last loss)."""
+    import torch
+    import torch.distributed as dist
+    for i in range(warmup):
+        job.step(*pool[i % len(pool)])
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        loss = job.step(*pool[i % len(pool)])
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if N > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item(), loss
+
+
+def timed_e2e(job, hosts, steps, sync_all, N, dev):
+    """End to end: every step copies its inputs from pinned host memory and its loss
+    is read back on the host.  Returns (ms total, max over ranks; last loss value)."""
+    import torch
+    import torch.distributed as dist
+    for i in range(2):
+        job.step(*job.to_device(*hosts[i % len(hosts)])).item()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    # every step: one pinned-host -> device copy of its inputs and one device ->
+    # host copy of its loss; the loss of step i is read on the host while step
+    # i+1 is already queued, so the host never stalls the launch stream
+    loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_ev = [torch.cuda.Event(), torch.cuda.Event()]
+    losses = []
+    for i, (x, y) in enumerate(job.stream_batches(hosts, steps)):
+        out = job.step(x, y)
+        loss_host[i & 1].copy_(out, non_blocking=True)
+        loss_ev[i & 1].record()
+        if i > 0:
+            loss_ev[(i - 1) & 1].synchronize()
+            losses.append(float(loss_host[(i - 1) & 1]))
+    loss_ev[(steps - 1) & 1].synchronize()
+    losses.append(float(loss_host[(steps - 1) & 1]))
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if N > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item(), losses[-1]
+
+
 def main():
     a = parse()
     if a.impl == "reference":
@@ -119,7 +184,8 @@ def main():
     import torch
     import torch.distributed as dist
     import hipress_b200 as hp
-    from hipress_b200.train.harness import HEADLINE, build_job
+    from hipress_b200.train.harness import HEADLINE, build_ddp_job, build_job
+    from hipress_b200.utils.verify import one_step_check, replicas_identical
 
     hp.init()
     N, rank = hp.size(), hp.rank()
@@ -129,8 +195,9 @@ def main():
     torch.backends.cuda.matmul.allow_tf32 = True
     torch.backends.cudnn.allow_tf32 = True
     head = HEADLINE[a.model]
+    plan = None if a.comprplan in (None, "", "none", "threshold") else a.comprplan
     over = dict(algorithm=a.comp_alg or head["algorithm"], topology=(a.topo or head["topology"]).lower(),
-                comp_threshold=a.comp_threshold, plan=a.comprplan, backend=a.sync_backend)
+                comp_threshold=a.comp_threshold, plan=plan, backend=a.sync_backend)
     if a.ctas:
         over["ctas"] = a.ctas
     if a.bucket_mb:
@@ -145,12 +212,16 @@ def main():
     job = build_job(a.model, cfg, batch=a.batch, seq_len=a.seq_len)
     eng = job.optimizer.engine
     dev = job.device
+    unit = "images/s" if job.kind == "image" else "samples/s"
 
     def sync_all():
         torch.cuda.synchronize()
         if N > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    global_batch = job.batch * N
+    per_s = lambda ms, steps: global_batch * steps / (ms * 1e-3)   # noqa: E731
 
     # ---------------- device-timed region: inputs already on the device -------------
     pool = [job.to_device(*job.host_batch(100 * rank + i)) for i in range(4)]
@@ -159,73 +230,75 @@ def main():
     sync_all()
     sampler = ClockSampler(physical_index(torch.cuda.current_device())) if rank == 0 else None
     l0 = eng.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(a.steps):
-        loss = job.step(*pool[i % 4])
-    e1.record()
-    sync_all()
-    ms = e0.elapsed_time(e1)
+    ms, loss = timed_steps(job, pool, a.steps, 0, sync_all, N, dev)
     launches = eng.launch_count - l0
     clocks = sampler.stop() if sampler else None
     eng.check()
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if N > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item()
-    global_batch = job.batch * N
-    value = global_batch * a.steps / (ms * 1e-3)
+    value = per_s(ms, a.steps)
 
     # ---------------- end to end: pinned host batch -> device every step, loss read back ----
     e2e = None
+    hosts = [job.host_batch(7000 + 100 * rank + i) for i in range(4)]
     if not a.no_e2e:
-        hosts = [job.host_batch(7000 + 100 * rank + i) for i in range(4)]
-        for i in range(2):
-            job.step(*job.to_device(*hosts[i % 4])).item()
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        # every step: one pinned-host -> device copy of its inputs and one device ->
-        # host copy of its loss; the loss of step i is read on the host while step
-        # i+1 is already queued, so the host never stalls the launch stream
-        loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
-        loss_ev = [torch.cuda.Event(), torch.cuda.Event()]
-        losses = []
-        for i, (x, y) in enumerate(job.stream_batches(hosts, a.steps)):
-            out = job.step(x, y)
-            loss_host[i & 1].copy_(out, non_blocking=True)
-            loss_ev[i & 1].record()
-            if i > 0:
-                loss_ev[(i - 1) & 1].synchronize()
-                losses.append(float(loss_host[(i - 1) & 1]))
-        loss_ev[(a.steps - 1) & 1].synchronize()
-        losses.append(float(loss_host[(a.steps - 1) & 1]))
-        lv = losses[-1]
-        e1.record()
-        sync_all()
-        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        if N > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e = {"value": round(global_batch * a.steps / (t.item() * 1e-3), 2),
-               "unit": "images/s" if job.kind == "image" else "samples/s",
-               "ms_per_step": round(t.item() / a.steps, 4),
+        t, lv = timed_e2e(job, hosts, a.steps, sync_all, N, dev)
+        e2e = {"value": round(per_s(t, a.steps), 2), "unit": unit,
+               "ms_per_step": round(t / a.steps, 4),
                "h2d_bytes_per_step": job.h2d_bytes(*hosts[0]), "d2h_bytes_per_step": 4,
                "last_loss": lv}
 
+    # ---------------- correctness evidence from the same run -------------------------
+    identical = replicas_identical(job.model)
+    check = one_step_check(job, *pool[0]) if not a.no_check else {}
+    eng.check()
+    st = eng.stats()
+    job.optimizer.close()
+    del job, eng
+    torch.cuda.empty_cache()
+
+    # ---------------- baseline arms, same process, same model / batch / steps --------
+    baselines = {}
+    if not a.no_baselines:
+        ddp = build_ddp_job(a.model, batch=a.batch, seq_len=a.seq_len)
+        t, _ = timed_steps(ddp, pool, a.steps, a.warmup, sync_all, N, dev)
+        baselines["ddp_images_s" if unit == "images/s" else "ddp_samples_s"] = round(per_s(t, a.steps), 2)
+        baselines["ddp_ms_per_step"] = round(t / a.steps, 4)
+        baselines["ratio_vs_ddp"] = round(value / per_s(t, a.steps), 4)
+        if e2e is not None:
+            t, _ = timed_e2e(ddp, hosts, a.steps, sync_all, N, dev)
+            baselines["ddp_e2e"] = round(per_s(t, a.steps), 2)
+            baselines["e2e_ratio_vs_ddp"] = round(e2e["value"] / per_s(t, a.steps), 4)
+        del ddp
+        torch.cuda.empty_cache()
+        if N > 1 and cfg.algorithm not in ("none", None, ""):
+            ucfg = hp.HipressConfig.from_env(**{**over, "backend": "host"})
+            unf = build_job(a.model, ucfg, batch=a.batch, seq_len=a.seq_len)
+            t, _ = timed_steps(unf, pool, a.steps, a.warmup, sync_all, N, dev)
+            baselines["unfused_images_s" if unit == "images/s" else "unfused_samples_s"] = \
+                round(per_s(t, a.steps), 2)
+            baselines["unfused_ms_per_step"] = round(t / a.steps, 4)
+            baselines["ratio_vs_unfused"] = round(value / per_s(t, a.steps), 4)
+            unf.optimizer.close()
+            del unf
+        baselines["what"] = ("ddp = torch DistributedDataParallel(gradient_as_bucket_view=True), NCCL, same "
+                             "model/batch/precision/optimizer (bare model at 1 GPU); unfused = this "
+                             "repo's schedule from separate encode/decode kernels around NCCL calls")
+
     if rank == 0:
-        st = eng.stats()
         line = {
-            "metric": ("images/sec" if job.kind == "image" else "samples/sec") +
+            "metric": ("images/sec" if unit == "images/s" else "samples/sec") +
                       f" {a.model} training step, device-timed, max over ranks",
-            "value": round(value, 2), "unit": "images/s" if job.kind == "image" else "samples/s",
+            "value": round(value, 2), "unit": unit,
             "n_gpus": N, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms / a.steps, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "weak",
+            # the reference publishes no throughput: the anchor is the torch-DDP arm of this run
+            "vs_baseline": baselines.get("ratio_vs_ddp"), "dtype": "bf16",
             "data": "synthetic (N(0,1) images / uniform token ids, random-init weights)",
             "impl": "hipress_b200",
-            "config": {"model": a.model, "global_batch": global_batch, "per_gpu_batch": job.batch,
-                       "seq_len": a.seq_len if job.kind != "image" else None,
+            "config": {"model": a.model, "global_batch": global_batch, "per_gpu_batch": global_batch // N,
+                       "seq_len": a.seq_len if unit != "images/s" else None,
                        "parallelism": f"dp{N}", "algorithm": cfg.algorithm, "topology": cfg.topology,
-                       "comp_threshold": cfg.comp_threshold, "sync_backend": eng.backend,
+                       "comp_threshold": cfg.comp_threshold, "plan": st["plan"],
+                       "plan_compressed_gradients": st["compressed_gradients"], "sync_backend": st["backend"],
                        "gradients": "fp32", "compressed_fraction":
                            round(st["compressed_elems"] / st["total_elems"], 4),
                        "buckets": st["buckets"], "ctas": cfg.ctas, "partition_sms": cfg.partition_sms,
@@ -234,9 +307,10 @@ def main():
                        "l2": "inputs larger than L2: weights+gradients+activations of one step "
                              "exceed the 126 MB L2 many times; no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": float(loss.item()),
+            "baselines": baselines, "replicas_identical": identical,
+            "one_step_rel_err": check.get("one_step_rel_err"), "one_step_check": check,
         }
         print(json.dumps(line))
-    job.optimizer.close()
     hp.shutdown()
     return 0
 

@@ -55,7 +55,7 @@ dense_encode_kernel(const float* __restrict__ g, float* __restrict__ r,
     }
     float meta[2];
     uint32_t frag[kIter];
-    encode_tile<ALG, B>(x, m, P, tensor_id, elem_offset + start, P.salt, s, meta, frag);
+    encode_tile<ALG, B>(x, m, P, tensor_id, elem_offset + start, P.salt, s, meta, frag, r != nullptr);
     if (r) store_tile(r + start, m, x);
     stage_frags<B>(s.codes, frag);
     __syncthreads();

@@ -122,12 +122,11 @@ __device__ __forceinline__ double block_sum(double v, TileSmem& s) {
   return t;
 }
 
+// Warp level: one redux.sync.{min,max}.f32 each (the fp32 forms of the warp
+// reduction are sm_100a instructions) instead of five shuffle + compare rounds.
 __device__ __forceinline__ void block_minmax(float& mn, float& mx, TileSmem& s) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  }
+  asm volatile("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(mn) : "f"(mn));
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(mx) : "f"(mx));
   if ((threadIdx.x & 31) == 0) {
     s.red_a[threadIdx.x >> 5] = mn;
     s.red_b[threadIdx.x >> 5] = mx;
@@ -162,8 +161,9 @@ __device__ __forceinline__ void decode_frag(uint32_t frag, const float (&meta)[2
 
 // Quantise the register tile x (m valid elements).  On return frag[] holds the
 // code fragments (zero for elements past m), meta[] the tile metadata, and x the
-// quantisation error x - decode(code) of every valid element.
-template <int ALG, int B, bool FULL>
+// quantisation error x - decode(code) of every valid element (left untouched by
+// TernGrad when the caller keeps no residual: want_err = false).
+template <int ALG, int B, bool FULL, bool ERR>
 __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, const DenseParams& P,
                                                  uint32_t tensor_id, uint64_t elem0, uint32_t salt,
                                                  TileSmem& s, float (&meta)[2],
@@ -198,13 +198,19 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
     gap = tern_gap(meta[0], meta[1], B);
     inv_gap = tern_inv_gap(gap);
   }
+  // TernGrad: one Philox call per pair of rows (see rnd16_counter); a tile that does
+  // not start on a 2048-element boundary of its tensor cannot share calls
+  const bool paired = ALG != kTernGrad || (elem0 & 2047u) == 0;
+  Philox4 rnd;
 #pragma unroll
   for (int j = 0; j < kIter; ++j) {
     const int i0 = 4 * (j * kThreads + (int)threadIdx.x);
-    Philox4 rnd;
+    uint32_t half = 0u;
     if (ALG == kTernGrad) {
       const uint64_t ge = elem0 + (uint64_t)i0;
-      rnd = philox4x32((uint32_t)(ge >> 2), tensor_id, P.step, salt, P.seed_lo, P.seed_hi);
+      half = paired ? (uint32_t)(j & 1) : rnd16_half(ge);
+      if (!paired || !(j & 1))
+        rnd = philox4x32(rnd16_counter(ge), tensor_id, P.step, salt, P.seed_lo, P.seed_hi);
     }
     uint32_t f = 0u;
 #pragma unroll
@@ -219,11 +225,11 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
           c = tbq_code(x[j][e], P.tau);
           d = tbq_value(c, P.tau);
         } else {
-          c = tern_code(x[j][e], meta[0], inv_gap, u01(rnd.v[e]), B);
-          d = tern_value(c, meta[0], gap);
+          c = tern_code(x[j][e], meta[0], inv_gap, u01_16(rnd.v[e], half), B);
+          d = ERR ? tern_value(c, meta[0], gap) : 0.0f;
         }
         f |= c << (e * B);
-        x[j][e] = x[j][e] - d;
+        if (ERR) x[j][e] = x[j][e] - d;
       }
     }
     frag[j] = f;
@@ -234,9 +240,14 @@ template <int ALG, int B>
 __device__ __forceinline__ void encode_tile(float (&x)[kIter][4], int m, const DenseParams& P,
                                             uint32_t tensor_id, uint64_t elem0, uint32_t salt,
                                             TileSmem& s, float (&meta)[2],
-                                            uint32_t (&frag)[kIter]) {
-  if (m == kTile) encode_tile_impl<ALG, B, true>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
-  else encode_tile_impl<ALG, B, false>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
+                                            uint32_t (&frag)[kIter], bool want_err = true) {
+  if (ALG == kTernGrad && !want_err) {
+    if (m == kTile) encode_tile_impl<ALG, B, true, false>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
+    else encode_tile_impl<ALG, B, false, false>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
+  } else {
+    if (m == kTile) encode_tile_impl<ALG, B, true, true>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
+    else encode_tile_impl<ALG, B, false, true>(x, m, P, tensor_id, elem0, salt, s, meta, frag);
+  }
 }
 
 // Byte layout of one dense payload of `n_layout` elements (n_layout fixes where

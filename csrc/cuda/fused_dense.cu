@@ -40,7 +40,7 @@ struct SegDev {
   uint32_t n;
   uint32_t chunk;        // elements per chunk, multiple of kTile
   uint32_t tiles;        // tiles per chunk
-  uint32_t tile_prefix;  // super-tiles (groups of kSuper tiles) of the segments before this one
+  uint32_t tile_prefix;  // tiles of one chunk of the segments before this one
   uint32_t pay_off;      // byte offset of this segment's chunk payload inside a slot
   uint32_t id;
 };
@@ -48,13 +48,13 @@ struct SegDev {
 struct BucketDev {
   SegDev seg[HP_MAX_SEGS];
   int nseg;
-  uint32_t tiles_total;  // super-tiles of one chunk summed over segments
+  uint32_t tiles_total;  // tiles of one chunk summed over segments = work items of a phase
   uint64_t slot_bytes;
 };
 
-// CTAs take work in groups of kSuper consecutive tiles so that the per-group
-// bookkeeping (which tensor, where, how many valid elements) is paid once.
-constexpr int kSuper = 4;
+// The decode phases take their tiles in groups of kGroup: the payload loads of a
+// whole group go out before the first one is waited for.
+constexpr int kGroup = 4;
 
 struct FusedParams {
   DenseParams P;
@@ -97,24 +97,38 @@ __device__ __forceinline__ uint2 ll_load(const uint2* slot) {
 
 // Spin (bounded) until the slot carries this launch's epoch.  `v` holds a first
 // load issued earlier so that several slots can be in flight before any spinning.
+// The top bit of the epoch word is the sender's "I gave up" mark: a CTA whose own
+// wait expired keeps sending (so nobody downstream has to wait out a timeout of
+// its own) but marks what it sends, and a receiver that sees the mark gives up at
+// once as well.  A CTA that has given up ("poisoned") touches neither the error
+// feedback state nor the gradient any more.
+constexpr uint32_t kGaveUp = 0x80000000u;
+
 __device__ __forceinline__ uint32_t ll_finish(const uint2* slot, uint2 v, const HpComm& cm,
                                               uint32_t* status, uint32_t code, WaitState& ws) {
   if (v.y == cm.epoch) return v.x;
   volatile int* poisoned = &ws.poisoned;
   if (*poisoned) return v.x;
-  const uint64_t t0 = global_timer_ns();
-  uint32_t polls = 0;
-  while (true) {
-    v = ll_load(slot);
-    if (v.y == cm.epoch) break;
-    // back off: thousands of threads polling L2 would slow the GEMMs of backward
-    // that run next to this kernel while a peer is late
-    if (polls > 4) __nanosleep(polls > 64 ? 400 : 100);
-    if ((++polls & 63u) == 0 && (*poisoned || global_timer_ns() - t0 > cm.timeout_ns)) {
-      atomicCAS(status, 0u, code);
-      *poisoned = 1;
-      break;
+  if ((v.y & ~kGaveUp) != cm.epoch) {
+    const uint64_t t0 = global_timer_ns();
+    uint32_t polls = 0;
+    while (true) {
+      v = ll_load(slot);
+      if ((v.y & ~kGaveUp) == cm.epoch) break;
+      // back off: thousands of threads polling L2 would slow the GEMMs of backward
+      // that run next to this kernel while a peer is late
+      if (polls > 4) __nanosleep(polls > 64 ? 400 : 100);
+      if ((++polls & 63u) == 0 && (*poisoned || global_timer_ns() - t0 > cm.timeout_ns)) {
+        atomicCAS(status, 0u, code);
+        *poisoned = 1;
+        break;
+      }
     }
+    if (cm.trace && threadIdx.x == 0) ws.spin_ns += global_timer_ns() - t0;
+  }
+  if (v.y == (cm.epoch | kGaveUp) && !*poisoned) {
+    atomicCAS(status, 0u, code | HP_STATUS_UPSTREAM);
+    *poisoned = 1;
   }
   return v.x;
 }
@@ -245,15 +259,26 @@ __device__ __forceinline__ PhaseSpec phase_spec(int ph, int N, int R) {
 
 struct TileRef {
   int seg;
-  uint32_t t0, cnt, nv;  // tiles t0 .. t0+cnt-1 of (seg, chunk); nv valid elements in the chunk
-  size_t off0;           // element offset of tile t0 inside the tensor
+  uint32_t t;   // tile of (seg, chunk)
+  int m;        // valid elements in the tile
+  size_t off;   // element offset of the tile inside the tensor
 };
 
-// Walks the super-tiles of one phase that belong to this CTA: super-tile
-// (tile_prefix + st) of the bucket goes to CTA (tile_prefix + st) % G.
+// Work distribution.  A launch is a sequence of phases (ring: N hops then N
+// gathers; PS: N pushes, the server pass, N pulls); every phase visits the
+// T = tiles_total tiles of one chunk of every tensor.  Tile i of phase ph is
+// work item ph * T + i, and item w belongs to CTA w % G: the assignment keeps
+// rotating across phases, so a bucket whose chunk has fewer tiles than there are
+// CTAs still spreads its phases over the whole grid (the CTAs of later hops wait
+// for their input while the earlier hops run elsewhere), and a chunk that is not
+// a multiple of G tiles leaves no CTA idle for a whole phase.  Every CTA takes its
+// items in increasing order, and an item only ever depends on a lower-numbered
+// item of another GPU, so the lowest unfinished item can always run: the grid must
+// fit the GPU (the launcher clamps it), nothing else is needed for progress.
 struct Cursor {
   int phase, seg, chunk;
-  uint32_t st, nvt, nv;  // next super-tile, valid tiles and valid elements of (seg, chunk)
+  uint32_t rot;          // (phase * T) % G
+  uint32_t t, nvt, nv;   // next tile, valid tiles and valid elements of (seg, chunk)
 };
 
 __device__ __forceinline__ void cursor_enter_seg(const BucketDev& bk, int G, int b, Cursor& c) {
@@ -261,8 +286,8 @@ __device__ __forceinline__ void cursor_enter_seg(const BucketDev& bk, int G, int
   const SegDev& sg = bk.seg[c.seg];
   c.nv = chunk_valid(sg.n, sg.chunk, c.chunk);
   c.nvt = (c.nv + kTile - 1) / kTile;
-  const uint32_t p = sg.tile_prefix % (uint32_t)G;
-  c.st = ((uint32_t)b + (uint32_t)G - p) % (uint32_t)G;
+  const uint32_t p = (c.rot + sg.tile_prefix) % (uint32_t)G;
+  c.t = ((uint32_t)b + (uint32_t)G - p) % (uint32_t)G;
 }
 
 __device__ __forceinline__ void cursor_begin(const BucketDev& bk, int G, int b, int phase,
@@ -270,34 +295,28 @@ __device__ __forceinline__ void cursor_begin(const BucketDev& bk, int G, int b, 
   c.phase = phase;
   c.chunk = chunk;
   c.seg = 0;
+  c.rot = (uint32_t)(((uint64_t)phase * bk.tiles_total) % (uint64_t)G);
   cursor_enter_seg(bk, G, b, c);
 }
 
-// next super-tile of the cursor's phase; false when the phase is exhausted
+// next tile of the cursor's phase that belongs to this CTA; false when the phase is exhausted
 __device__ __forceinline__ bool cursor_next(const BucketDev& bk, int G, int b, Cursor& c,
                                             TileRef& out) {
   while (c.seg < bk.nseg) {
-    const uint32_t t0 = c.st * kSuper;
-    if (t0 < c.nvt) {
+    if (c.t < c.nvt) {
       const SegDev& sg = bk.seg[c.seg];
-      const uint32_t rest = c.nvt - t0;
+      const uint32_t left = c.nv - c.t * kTile;
       out.seg = c.seg;
-      out.t0 = t0;
-      out.cnt = rest < (uint32_t)kSuper ? rest : (uint32_t)kSuper;
-      out.nv = c.nv;
-      out.off0 = (size_t)c.chunk * sg.chunk + (size_t)t0 * kTile;
-      c.st += (uint32_t)G;
+      out.t = c.t;
+      out.m = (int)(left < (uint32_t)kTile ? left : (uint32_t)kTile);
+      out.off = (size_t)c.chunk * sg.chunk + (size_t)c.t * kTile;
+      c.t += (uint32_t)G;
       return true;
     }
     ++c.seg;
     cursor_enter_seg(bk, G, b, c);
   }
   return false;
-}
-
-__device__ __forceinline__ int tile_valid(const TileRef& tr, uint32_t u) {
-  const uint32_t left = tr.nv - (tr.t0 + u) * kTile;
-  return (int)(left < (uint32_t)kTile ? left : (uint32_t)kTile);
 }
 
 // a tile can be prefetched with a bulk copy when it is full and 16-byte aligned
@@ -313,6 +332,28 @@ __device__ __forceinline__ void load_tile_smem(const float* sp, float (&x)[kIter
   }
 }
 
+// device-side timestamps (see HpComm.trace): word 0 first CTA start (min), 1 end of
+// the last encode phase (max), 2 kernel end (max), 3 epoch, 4+ph end of phase ph
+// (max over CTAs), 4+HP_TRACE_PHASES+ph nanoseconds thread 0 of every CTA spent
+// polling for input in phase ph (sum over CTAs)
+__device__ __forceinline__ void trace_mark(const HpComm& cm, int E, int which) {
+  if (cm.trace && threadIdx.x == 0) {
+    unsigned long long* t = reinterpret_cast<unsigned long long*>(cm.trace) + HP_TRACE_WORDS * E;
+    const unsigned long long now = global_timer_ns();
+    if (which == 0) atomicMin(t, now);
+    else atomicMax(t + which, now);
+    if (which == 2) t[3] = cm.epoch;
+  }
+}
+__device__ __forceinline__ void trace_phase(const HpComm& cm, int E, int ph, WaitState& ws) {
+  if (cm.trace && threadIdx.x == 0 && ph < HP_TRACE_PHASES) {
+    unsigned long long* t = reinterpret_cast<unsigned long long*>(cm.trace) + HP_TRACE_WORDS * E;
+    atomicMax(t + 4 + ph, (unsigned long long)global_timer_ns());
+    atomicAdd(t + 4 + HP_TRACE_PHASES + ph, (unsigned long long)ws.spin_ns);
+    ws.spin_ns = 0;
+  }
+}
+
 template <int ALG, int B, int TOPO>
 __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm& cm,
                                               const FusedParams& fp, FusedSmem& sm, int R, int E,
@@ -324,11 +365,6 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
   // prefetcher state: runs ahead of the consumer over the same tile sequence
   Cursor prod;
   cursor_begin(bk, G, b, 0, phase_spec<TOPO>(0, N, R).chunk, prod);
-  TileRef pr;
-  pr.cnt = 0;
-  uint32_t pu = 0;           // next tile inside pr
-  const float* pg = nullptr; // g / r addresses of tile pu of pr
-  const float* prr = nullptr;
   bool prod_more = true;
   uint32_t issued = 0, consumed = 0;  // tiles prefetched / used through the bulk pipeline
 
@@ -347,143 +383,135 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
     TileRef tr;
     while (cursor_next(bk, G, b, cons, tr)) {
       const SegDev& sg = bk.seg[tr.seg];
-      const float* gp0 = sg.g + E * cm.emu_stride_g + tr.off0;
-      float* rp0 = sg.r ? sg.r + E * cm.emu_stride_r + tr.off0 : nullptr;
-      const bool aligned =
-          ((reinterpret_cast<uintptr_t>(gp0) | reinterpret_cast<uintptr_t>(rp0)) & 15) == 0;
-      for (uint32_t u = 0; u < tr.cnt; ++u) {
-        // top up the prefetch pipeline (stages of finished tiles are free: the
-        // previous tile ended with a CTA barrier)
-        while (prod_more && issued - consumed < kStages) {
-          if (pu >= pr.cnt) {
-            bool got = cursor_next(bk, G, b, prod, pr);
-            while (!got && prod.phase + 1 < N) {  // run ahead across phases
-              cursor_begin(bk, G, b, prod.phase + 1,
-                           phase_spec<TOPO>(prod.phase + 1, N, R).chunk, prod);
-              got = cursor_next(bk, G, b, prod, pr);
-            }
-            if (!got) {
-              prod_more = false;
-              break;
-            }
-            const SegDev& psg = bk.seg[pr.seg];
-            pg = psg.g + E * cm.emu_stride_g + pr.off0;
-            prr = psg.r ? psg.r + E * cm.emu_stride_r + pr.off0 : nullptr;
-            pu = 0;
+      // top up the prefetch pipeline (stages of finished tiles are free: the
+      // previous tile ended with a CTA barrier)
+      while (prod_more && issued - consumed < kStages) {
+        TileRef pr;
+        bool got = cursor_next(bk, G, b, prod, pr);
+        while (!got && prod.phase + 1 < N) {  // run ahead across phases
+          cursor_begin(bk, G, b, prod.phase + 1, phase_spec<TOPO>(prod.phase + 1, N, R).chunk,
+                       prod);
+          got = cursor_next(bk, G, b, prod, pr);
+        }
+        if (!got) {
+          prod_more = false;
+          break;
+        }
+        const SegDev& psg = bk.seg[pr.seg];
+        const float* pg = psg.g + E * cm.emu_stride_g + pr.off;
+        const float* prr = psg.r ? psg.r + E * cm.emu_stride_r + pr.off : nullptr;
+        if (bulk_ok(pg, prr, pr.m)) {
+          if (threadIdx.x == 0) {
+            const int st = issued % kStages;
+            mbar_expect_tx(&sm.full[st], (prr ? 2u : 1u) * kTile * 4u);
+            bulk_load(sm.g[st], pg, kTile * 4u, &sm.full[st]);
+            if (prr) bulk_load(sm.r[st], prr, kTile * 4u, &sm.full[st]);
           }
-          if (bulk_ok(pg, prr, tile_valid(pr, pu))) {
-            if (threadIdx.x == 0) {
-              const int st = issued % kStages;
-              mbar_expect_tx(&sm.full[st], (prr ? 2u : 1u) * kTile * 4u);
-              bulk_load(sm.g[st], pg, kTile * 4u, &sm.full[st]);
-              if (prr) bulk_load(sm.r[st], prr, kTile * 4u, &sm.full[st]);
-            }
-            ++issued;
-          }
-          ++pu;
-          pg += kTile;
-          if (prr) prr += kTile;
+          ++issued;
         }
-        const int m = tile_valid(tr, u);
-        const uint32_t t = tr.t0 + u;
-        const float* gp = gp0 + (size_t)u * kTile;
-        float* rp = rp0 ? rp0 + (size_t)u * kTile : nullptr;
-        float x[kIter][4];
-        // first loads of the incoming payload go out before anything waits
-        TileRx<ALG, B> rx;
-        if (in_base) recv_issue<ALG, B>(in_base + sg.pay_off, t, rx);
-        const bool bulk = aligned && m == kTile;
-        int st = 0;
-        if (bulk) {
-          st = consumed % kStages;
-          if (!sm.ws.poisoned &&
-              !mbar_wait_bounded(&sm.full[st], (consumed / kStages) & 1, cm.timeout_ns, status,
-                                 HP_STATUS_TIMEOUT | (3u << 16) | (b & 255)))
-            sm.ws.poisoned = 1;
-          ++consumed;
-          load_tile_smem(sm.g[st], x);
-        } else {
-          load_tile(gp, m, x);
-        }
-        if (in_base) {
-          float d[kIter][4];
-          recv_finish<ALG, B>(in_base + sg.pay_off, t, rx, cm, status,
-                              HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
-                              sm.ws, fp.P.tau, d);
-#pragma unroll
-          for (int j = 0; j < kIter; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] + d[j][e];
-        }
-        if (rp) {
-          float rr[kIter][4];
-          if (bulk) load_tile_smem(sm.r[st], rr);
-          else load_tile(rp, m, rr);
-#pragma unroll
-          for (int j = 0; j < kIter; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) x[j][e] = rr[j][e] + x[j][e];
-        }
-        float meta[2];
-        uint32_t frag[kIter];
-        encode_tile<ALG, B>(x, m, fp.P, sg.id, tr.off0 + (size_t)u * kTile, fp.P.salt + ps.salt,
-                            sm.tile, meta, frag);
-        if (rp) store_tile(rp, m, x);
-        uint32_t words[LL<B>::W];
-        pack_words<B>(frag, words);
-#pragma unroll
-        for (int q = 0; q < HP_MAX_RANKS; ++q)
-          if (q < ps.ndst) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, cm.epoch);
-        __syncthreads();  // the prefetch stage of this tile may be refilled from here on
       }
+      const int m = tr.m;
+      const uint32_t t = tr.t;
+      const float* gp = sg.g + E * cm.emu_stride_g + tr.off;
+      float* rp = sg.r ? sg.r + E * cm.emu_stride_r + tr.off : nullptr;
+      float x[kIter][4];
+      // first loads of the incoming payload go out before anything waits
+      TileRx<ALG, B> rx;
+      if (in_base) recv_issue<ALG, B>(in_base + sg.pay_off, t, rx);
+      const bool bulk = bulk_ok(gp, rp, m);
+      int st = 0;
+      if (bulk) {
+        st = consumed % kStages;
+        if (!sm.ws.poisoned &&
+            !mbar_wait_bounded(&sm.full[st], (consumed / kStages) & 1, cm.timeout_ns, status,
+                               HP_STATUS_TIMEOUT | (3u << 16) | (b & 255)))
+          sm.ws.poisoned = 1;
+        ++consumed;
+        load_tile_smem(sm.g[st], x);
+      } else {
+        load_tile(gp, m, x);
+      }
+      if (in_base) {
+        float d[kIter][4];
+        recv_finish<ALG, B>(in_base + sg.pay_off, t, rx, cm, status,
+                            HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
+                            sm.ws, fp.P.tau, d);
+#pragma unroll
+        for (int j = 0; j < kIter; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] + d[j][e];
+      }
+      if (rp) {
+        float rr[kIter][4];
+        if (bulk) load_tile_smem(sm.r[st], rr);
+        else load_tile(rp, m, rr);
+#pragma unroll
+        for (int j = 0; j < kIter; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[j][e] = rr[j][e] + x[j][e];
+      }
+      float meta[2];
+      uint32_t frag[kIter];
+      encode_tile<ALG, B>(x, m, fp.P, sg.id, tr.off, fp.P.salt + ps.salt, sm.tile, meta, frag,
+                          rp != nullptr);
+      // after an expired wait the merged input is not a real partial sum: the error
+      // feedback state keeps its last good contents
+      if (rp && !*(volatile int*)&sm.ws.poisoned) store_tile(rp, m, x);
+      uint32_t words[LL<B>::W];
+      pack_words<B>(frag, words);
+      const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
+#pragma unroll
+      for (int q = 0; q < HP_MAX_RANKS; ++q)
+        if (q < ps.ndst) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
+      __syncthreads();  // the prefetch stage of this tile may be refilled from here on
     }
+    trace_phase(cm, E, ph, sm.ws);
   }
 }
 
-// decode the reduced chunk `c` that arrives in inbox slot `slot` into the gradient
+// decode the reduced chunk `c` that arrives in inbox slot `slot` into the gradient;
+// `phase` continues the work-item numbering of the encode phases
 template <int ALG, int B>
 __device__ __forceinline__ void decode_phase(const BucketDev& bk, const HpComm& cm,
                                              const FusedParams& fp, FusedSmem& sm, int R, int E,
-                                             int slot, int c, uint32_t* status) {
+                                             int phase, int slot, int c, uint32_t* status) {
   const int G = (int)gridDim.x;
   const int b = (int)blockIdx.x;
   const uint8_t* sp = reinterpret_cast<const uint8_t*>(cm.inbox[R]) + (size_t)slot * bk.slot_bytes;
   const uint32_t code = HP_STATUS_TIMEOUT | (2u << 16) | ((uint32_t)slot << 8) | (b & 255);
   Cursor cur;
-  cursor_begin(bk, G, b, 0, c, cur);
-  TileRef tr;
-  while (cursor_next(bk, G, b, cur, tr)) {
-    const SegDev& sg = bk.seg[tr.seg];
-    float* op = sg.out + E * cm.emu_stride_out + tr.off0;
-    // first loads of the whole super-tile go out before anything spins
-    TileRx<ALG, B> rx[kSuper];
+  cursor_begin(bk, G, b, phase, c, cur);
+  bool more = true;
+  while (more) {
+    // first loads of a whole group of tiles go out before anything spins
+    TileRef tr[kGroup];
+    TileRx<ALG, B> rx[kGroup];
+    int cnt = 0;
 #pragma unroll
-    for (uint32_t u = 0; u < (uint32_t)kSuper; ++u)
-      if (u < tr.cnt) recv_issue<ALG, B>(sp + sg.pay_off, tr.t0 + u, rx[u]);
+    for (int u = 0; u < kGroup; ++u) {
+      if (more) {
+        more = cursor_next(bk, G, b, cur, tr[u]);
+        if (more) {
+          recv_issue<ALG, B>(sp + bk.seg[tr[u].seg].pay_off, tr[u].t, rx[u]);
+          cnt = u + 1;
+        }
+      }
+    }
 #pragma unroll
-    for (uint32_t u = 0; u < (uint32_t)kSuper; ++u) {
-      if (u < tr.cnt) {
-        const int m = tile_valid(tr, u);
+    for (int u = 0; u < kGroup; ++u) {
+      if (u < cnt) {
+        const SegDev& sg = bk.seg[tr[u].seg];
         float x[kIter][4];
-        recv_finish<ALG, B>(sp + sg.pay_off, tr.t0 + u, rx[u], cm, status, code, sm.ws, fp.P.tau, x);
+        recv_finish<ALG, B>(sp + sg.pay_off, tr[u].t, rx[u], cm, status, code, sm.ws, fp.P.tau, x);
 #pragma unroll
         for (int j = 0; j < kIter; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] * fp.inv_n;
-        store_tile(op + (size_t)u * kTile, m, x);
+        // a tile whose payload never arrived is left as it was (the local gradient)
+        if (!*(volatile int*)&sm.ws.poisoned)
+          store_tile(sg.out + E * cm.emu_stride_out + tr[u].off, tr[u].m, x);
       }
     }
-  }
-}
-
-// device-side timestamps (see HpComm.trace)
-__device__ __forceinline__ void trace_mark(const HpComm& cm, int E, int which) {
-  if (cm.trace && threadIdx.x == 0) {
-    unsigned long long* t = reinterpret_cast<unsigned long long*>(cm.trace) + 4 * E;
-    const unsigned long long now = global_timer_ns();
-    if (which == 0) atomicMin(t, now);
-    else atomicMax(t + which, now);
-    if (which == 2) t[3] = cm.epoch;
   }
 }
 
@@ -492,6 +520,7 @@ __device__ __forceinline__ void fused_prologue(FusedSmem& sm) {
     for (int i = 0; i < kStages; ++i) mbar_init(&sm.full[i], 1);
     mbar_init_fence();
     sm.ws.poisoned = 0;
+    sm.ws.spin_ns = 0;
   }
   __syncthreads();
 }
@@ -513,7 +542,8 @@ ring_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   // gather: rank src finalised chunk src+1
   for (int qq = 0; qq < N; ++qq) {
     const int src = (R + qq) % N;
-    decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N - 1 + src, (src + 1) % N, status);
+    decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N + qq, N - 1 + src, (src + 1) % N, status);
+    trace_phase(cm, E, N + qq, sm.ws);
   }
   trace_mark(cm, E, 2);
 }
@@ -535,14 +565,14 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
   fused_prologue(sm);
   trace_mark(cm, E, 0);
 
-  // phase 1: push
+  // phases 0 .. N-1: push
   encode_phases<ALG, B, HP_TOPO_PS>(bk, cm, fp, sm, R, E, status);
   trace_mark(cm, E, 1);
 
-  // phase 2: server for chunk R: sum the N payloads in rank order, re-encode, broadcast
+  // phase N: server for chunk R: sum the N payloads in rank order, re-encode, broadcast
   {
     Cursor cur;
-    cursor_begin(bk, G, b, 0, R, cur);
+    cursor_begin(bk, G, b, N, R, cur);
     TileRef tr;
     uint8_t* dst_base[HP_MAX_RANKS];
 #pragma unroll
@@ -552,55 +582,56 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
                           : nullptr;
     while (cursor_next(bk, G, b, cur, tr)) {
       const SegDev& sg = bk.seg[tr.seg];
-      for (uint32_t u = 0; u < tr.cnt; ++u) {
-        const int m = tile_valid(tr, u);
-        const uint32_t t = tr.t0 + u;
-        const size_t coff = (size_t)t * kTile;  // offset inside the owned chunk
-        float x[kIter][4];
-        // the N pushes are polled two at a time: loads of the next source are in
-        // flight while the current one is decoded
-        TileRx<ALG, B> rx[2];
-        recv_issue<ALG, B>(my_inbox + sg.pay_off, t, rx[0]);
-        for (int q = 0; q < N; ++q) {
-          if (q + 1 < N)
-            recv_issue<ALG, B>(my_inbox + (size_t)(q + 1) * bk.slot_bytes + sg.pay_off, t,
-                               rx[(q + 1) & 1]);
-          float d[kIter][4];
-          recv_finish<ALG, B>(my_inbox + (size_t)q * bk.slot_bytes + sg.pay_off, t, rx[q & 1], cm,
-                              status, HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)q << 8) | (b & 255),
-                              sm.ws, fp.P.tau, d);
+      const int m = tr.m;
+      const uint32_t t = tr.t;
+      const size_t coff = (size_t)t * kTile;  // offset inside the owned chunk
+      float x[kIter][4];
+      // the N pushes are polled two at a time: loads of the next source are in
+      // flight while the current one is decoded
+      TileRx<ALG, B> rx[2];
+      recv_issue<ALG, B>(my_inbox + sg.pay_off, t, rx[0]);
+      for (int q = 0; q < N; ++q) {
+        if (q + 1 < N)
+          recv_issue<ALG, B>(my_inbox + (size_t)(q + 1) * bk.slot_bytes + sg.pay_off, t,
+                             rx[(q + 1) & 1]);
+        float d[kIter][4];
+        recv_finish<ALG, B>(my_inbox + (size_t)q * bk.slot_bytes + sg.pay_off, t, rx[q & 1], cm,
+                            status, HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)q << 8) | (b & 255),
+                            sm.ws, fp.P.tau, d);
 #pragma unroll
-          for (int j = 0; j < kIter; ++j)
+        for (int j = 0; j < kIter; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) x[j][e] = q > 0 ? x[j][e] + d[j][e] : d[j][e];
-        }
-        float* rp = sg.sr ? sg.sr + E * cm.emu_stride_sr + coff : nullptr;
-        if (rp) {
-          float rr[kIter][4];
-          load_tile(rp, m, rr);
-#pragma unroll
-          for (int jj = 0; jj < kIter; ++jj)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) x[jj][e] = rr[jj][e] + x[jj][e];
-        }
-        float meta[2];
-        uint32_t frag[kIter];
-        encode_tile<ALG, B>(x, m, fp.P, sg.id, (size_t)R * sg.chunk + coff,
-                            fp.P.salt + (uint32_t)(R * 256 + 1), s, meta, frag);
-        if (rp) store_tile(rp, m, x);
-        uint32_t words[LL<B>::W];
-        pack_words<B>(frag, words);
-#pragma unroll
-        for (int q = 0; q < HP_MAX_RANKS; ++q)
-          if (q < N) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, cm.epoch);
+          for (int e = 0; e < 4; ++e) x[j][e] = q > 0 ? x[j][e] + d[j][e] : d[j][e];
       }
+      float* rp = sg.sr ? sg.sr + E * cm.emu_stride_sr + coff : nullptr;
+      if (rp) {
+        float rr[kIter][4];
+        load_tile(rp, m, rr);
+#pragma unroll
+        for (int jj = 0; jj < kIter; ++jj)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[jj][e] = rr[jj][e] + x[jj][e];
+      }
+      float meta[2];
+      uint32_t frag[kIter];
+      encode_tile<ALG, B>(x, m, fp.P, sg.id, (size_t)R * sg.chunk + coff,
+                          fp.P.salt + (uint32_t)(R * 256 + 1), s, meta, frag, rp != nullptr);
+      if (rp && !*(volatile int*)&sm.ws.poisoned) store_tile(rp, m, x);
+      uint32_t words[LL<B>::W];
+      pack_words<B>(frag, words);
+      const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
+#pragma unroll
+      for (int q = 0; q < HP_MAX_RANKS; ++q)
+        if (q < N) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
     }
+    trace_phase(cm, E, N, sm.ws);
   }
 
-  // phase 3: pull: decode every owner's reduced chunk
+  // phases N+1 .. 2N: pull: decode every owner's reduced chunk
   for (int i = 0; i < N; ++i) {
     const int j = (R + i) % N;
-    decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N + j, j, status);
+    decode_phase<ALG, B>(bk, cm, fp, sm, R, E, N + 1 + i, N + j, j, status);
+    trace_phase(cm, E, N + 1 + i, sm.ws);
   }
   trace_mark(cm, E, 2);
 }
@@ -623,10 +654,10 @@ static int build_bucket(int alg, int bits, const HpSeg* segs, int nseg, int nran
     d.n = (uint32_t)n;
     d.chunk = (uint32_t)chunk;
     d.tiles = (uint32_t)(chunk / kTile);
-    d.tile_prefix = (uint32_t)tiles;  // counted in super-tiles
+    d.tile_prefix = (uint32_t)tiles;
     d.pay_off = (uint32_t)pay;
     d.id = segs[i].id;
-    tiles += (d.tiles + kSuper - 1) / kSuper;
+    tiles += d.tiles;
     {
       const uint64_t words = bits <= 2 ? 1 : bits / 2;
       const uint64_t slots = dense_meta_floats(alg) + words * kThreads;  // per tile
@@ -643,6 +674,10 @@ static int build_bucket(int alg, int bits, const HpSeg* segs, int nseg, int nran
 static int num_slots(int topo, int nranks) {
   return topo == HP_TOPO_RING ? 2 * nranks - 1 : 2 * nranks;
 }
+// phases of one launch (see Cursor)
+static int num_phases(int topo, int nranks) {
+  return topo == HP_TOPO_RING ? 2 * nranks : 2 * nranks + 1;
+}
 
 template <int ALG, int B>
 static int launch_fused(int topo, const BucketDev& bk, const HpComm& cm, const FusedParams& fp,
@@ -650,28 +685,35 @@ static int launch_fused(int topo, const BucketDev& bk, const HpComm& cm, const F
   void (*kern)(const BucketDev, const HpComm, const FusedParams) =
       topo == HP_TOPO_RING ? ring_dense_kernel<ALG, B> : ps_dense_kernel<ALG, B>;
   const size_t smem = sizeof(FusedSmem);
-  static bool attr_set[2][64] = {};  // per (topology, device): the attribute is sticky
-  int cur_dev = 0;
-  cudaGetDevice(&cur_dev);
-  if (cur_dev < 0 || cur_dev >= 64 || !attr_set[topo][cur_dev]) {
-    cudaError_t e0 = cudaFuncSetAttribute((const void*)kern,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e0 != cudaSuccess) return (int)e0;
-    if (cur_dev >= 0 && cur_dev < 64) attr_set[topo][cur_dev] = true;
-  }
-  if (cm.emulate) {
-    int dev = 0, sms = 0, per_sm = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+  // per (topology, device): the shared-memory attribute is sticky, and the number of
+  // CTAs the GPU can hold at once does not change
+  static int resident[2][64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  int cap = (dev >= 0 && dev < 64) ? resident[topo][dev] : 0;
+  if (cap == 0) {
+    e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
     if (e != cudaSuccess) return (int)e;
+    int sms = 0, per_sm = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
     if (e != cudaSuccess) return (int)e;
-    if ((long long)ctas * cm.nranks > (long long)per_sm * sms) return HP_ERR_RESIDENCY;
+    cap = per_sm * sms;
+    if (cap < 1) return HP_ERR_RESIDENCY;
+    if (dev >= 0 && dev < 64) resident[topo][dev] = cap;
+  }
+  if (cm.emulate) {
+    if ((long long)ctas * cm.nranks > (long long)cap) return HP_ERR_RESIDENCY;
     void* args[] = {(void*)&bk, (void*)&cm, (void*)&fp};
     e = cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas, cm.nranks), dim3(kThreads),
                                     args, smem, st);
     return (int)e;
   }
+  // a CTA may wait for a peer's CTA of any index (the work items rotate over the
+  // grid), so the whole grid has to fit the GPU once nothing else runs on it
+  if (ctas > cap) ctas = cap;
   kern<<<dim3(ctas, 1), kThreads, smem, st>>>(bk, cm, fp);
   return (int)cudaGetLastError();
 }
@@ -697,12 +739,6 @@ int hp_fused_dense_layout(int topo, int alg, int bits, const uint64_t* ns, int n
   return 0;
 }
 
-// uint32 flag words reserved per rank (kept for layout compatibility; the dense
-// kernels signal inside the payload slots)
-uint64_t hp_fused_flag_words(int topo, int nranks, int ctas) {
-  return (uint64_t)num_slots(topo, nranks) * (uint64_t)ctas;
-}
-
 // elements of the server residual a PS owner keeps for a tensor of n elements
 uint64_t hp_fused_chunk_elems(uint64_t n, int nranks) {
   return align_up((n + nranks - 1) / nranks, kTile);
@@ -716,7 +752,10 @@ int hp_cuda_fused_dense(int topo, int alg, int bits, const HpSeg* segs, int nseg
   BucketDev bk;
   int rc = build_bucket(alg, bits, segs, nseg, comm->nranks, bk);
   if (rc) return rc;
-  if ((uint32_t)ctas > bk.tiles_total) ctas = (int)bk.tiles_total;
+  {  // never more CTAs than work items
+    const uint64_t items = (uint64_t)bk.tiles_total * (uint64_t)num_phases(topo, comm->nranks);
+    if ((uint64_t)ctas > items) ctas = (int)items;
+  }
   FusedParams fp;
   fp.P = DenseParams{tau, step, salt, (uint32_t)seed, (uint32_t)(seed >> 32)};
   fp.inv_n = 1.0f / (float)comm->nranks;

@@ -26,10 +26,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 struct WaitState {
   int poisoned;
+  unsigned long long spin_ns;  // time thread 0 spent polling (only kept when tracing)
 };
 
 __device__ __forceinline__ void wait_init(WaitState& ws) {
-  if (threadIdx.x == 0) ws.poisoned = 0;
+  if (threadIdx.x == 0) {
+    ws.poisoned = 0;
+    ws.spin_ns = 0;
+  }
   __syncthreads();
 }
 

@@ -17,9 +17,14 @@
 #define HP_TOPO_RING 0
 #define HP_TOPO_PS 1
 
+// device-side trace of the fused dense kernels (HpComm.trace): uint64 words per rank
+#define HP_TRACE_PHASES 20
+#define HP_TRACE_WORDS (4 + 2 * HP_TRACE_PHASES)
+
 // status words written by a kernel whose bounded wait expired
 #define HP_STATUS_OK 0u
 #define HP_STATUS_TIMEOUT 0x80000000u  // | (phase << 16) | (slot << 8) | cta
+#define HP_STATUS_UPSTREAM 0x40000000u  // or-ed in: the sender of this input had given up first
 
 #ifdef __cplusplus
 extern "C" {
@@ -48,9 +53,11 @@ typedef struct {
   void* status;                // this rank's status words (emulate: nranks * 4 words)
   // emulation only: element strides between consecutive ranks' copies of g / r / out / sr
   int64_t emu_stride_g, emu_stride_r, emu_stride_out, emu_stride_sr;
-  // optional device-side timing of the fused dense kernels: 4 uint64 per rank played by
-  // the launch {first CTA start (min), last encode phase end (max), last CTA end (max),
-  // epoch}, %globaltimer nanoseconds; the host presets {UINT64_MAX, 0, 0, 0}.  NULL = off.
+  // optional device-side timing of the fused dense kernels: HP_TRACE_WORDS uint64 per rank
+  // played by the launch {first CTA start (min), last encode phase end (max), last CTA end
+  // (max), epoch, end of phase p (max over CTAs) x HP_TRACE_PHASES, time spent polling for
+  // input in phase p (thread 0, summed over CTAs) x HP_TRACE_PHASES}, %globaltimer
+  // nanoseconds; the host presets {UINT64_MAX, 0, 0, ...}.  NULL = off.
   void* trace;
 } HpComm;
 

@@ -120,6 +120,19 @@ HP_HD Philox4 philox4x32(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
 // uniform in [0,1) with 24 bits, exact in fp32 on host and device
 HP_HD float u01(uint32_t r) { return (float)(r >> 8) * (1.0f / 16777216.0f); }
 
+// Stochastic rounding draws (TernGrad): 16-bit uniforms, so one Philox call serves
+// eight elements -- the four elements of float4 number q = elem >> 2 and of float4
+// q + 256, which are two consecutive rows of one thread of a 4096-element tile.  The
+// call is keyed by q with bit 8 cleared; float4 q takes the low halves of the four
+// words when its bit 8 is clear and the high halves when it is set.  A pure function
+// of the element index, so the CPU oracle and every kernel layout draw the same
+// numbers.  Sixteen bits bound the rounding bias by 2^-17 of a quantisation step.
+HP_HD uint32_t rnd16_counter(uint64_t elem) { return (uint32_t)(elem >> 2) & ~256u; }
+HP_HD uint32_t rnd16_half(uint64_t elem) { return (uint32_t)(elem >> 10) & 1u; }
+HP_HD float u01_16(uint32_t word, uint32_t half) {
+  return (float)((word >> (16u * half)) & 0xFFFFu) * (1.0f / 65536.0f);
+}
+
 // ---------------------------------------------------------------------------
 // Parameters shared by every dense (quantising) algorithm
 // ---------------------------------------------------------------------------

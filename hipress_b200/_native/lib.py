@@ -123,7 +123,6 @@ def cuda():
          C.c_float, C.c_int, C.c_int, vp)
     _sig(L.hp_fused_dense_layout, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_uint64),
          C.c_int, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32))
-    _sig(L.hp_fused_flag_words, C.c_uint64, C.c_int, C.c_int, C.c_int)
     _sig(L.hp_fused_chunk_elems, C.c_uint64, C.c_uint64, C.c_int)
     _sig(L.hp_cuda_fused_dense, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(HpSeg), C.c_int,
          C.POINTER(HpComm), C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, vp)

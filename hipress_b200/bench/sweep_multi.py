@@ -4,7 +4,7 @@
 For fp32 gradients of 4 KB - 1 GB (powers of 4, N(0,1), seed 0 + rank) and each of
 onebit, TBQ, TernGrad, DGC 0.1 %, GradDrop 0.1 % through Ring and PS it times
 
-* ``fused``     the fused kernels (dense: ring and PS; sparse: PS),
+* ``fused``     the fused kernels (every algorithm through ring and PS),
 * ``unfused``   the same schedule from separate encode / decode kernels around NCCL
                 point-to-point and all-gather calls (the reference's structure),
 * ``allreduce`` the uncompressed NCCL all-reduce of the same gradient,
@@ -66,6 +66,9 @@ def main(argv=None):
     ap.add_argument("--ctas", type=int, default=444)
     ap.add_argument("--algs", default="onebit,tbq,terngrad,dgc,graddrop")
     ap.add_argument("--skip-unfused", action="store_true")
+    ap.add_argument("--trace", action="store_true",
+                    help="dense kernels: one more launch per row with the device-side phase trace "
+                         "(when the last CTA left each hop, and how long CTAs polled for input)")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
     comm.init()
@@ -126,6 +129,17 @@ def main(argv=None):
                     roof = roofline_ms(comp, n, N, topo, peaks)
                     row.update({k: round(v, 5) for k, v in roof.items()})
                     row["roofline_frac"] = round(roof["roof_ms"] / row["fused_ms"], 4)
+                    if a.trace and not comp.spec.sparse:
+                        fused.enable_trace()
+                        work.copy_(g)
+                        torch.cuda.synchronize()
+                        dist.barrier() if N > 1 else None
+                        fn()
+                        torch.cuda.synchronize()
+                        row["trace_rank0"] = [{"phase": p["phase"], "end_ms": round(p["end_ms"], 4),
+                                               "mean_poll_ms": round(p["mean_poll_ms"], 4)}
+                                              for p in fused.last_trace_phases()[0]]
+                        fused.enable_trace(False)
                     if int(status.abs().sum()) != 0:
                         row["status"] = [w & 0xFFFFFFFF for w in status.tolist()]
                         status.zero_()

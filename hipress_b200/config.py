@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import argparse
 import os
+import typing
 from dataclasses import dataclass, field, fields
 
 
@@ -29,6 +30,7 @@ class HipressConfig:
     partition_sms: int = 0            # SMs reserved (green context) for fused kernels that overlap backward; 0 = off
     partition_ctas: int = 48          # CTAs of a fused kernel on the SM partition
     timeout_s: float = 10.0           # bound of every device-side wait
+    strict_status: bool = False       # synchronize() waits for the step's kernels and raises on an expired wait before the optimizer runs
     server_residual: bool = True      # PS: error feedback on the re-encode at the owner
     hierarchical: str = "auto"        # job on several machines: auto | on | off (see GradSyncEngine)
     overlap: bool = True              # launch buckets from gradient hooks during backward
@@ -42,16 +44,22 @@ class HipressConfig:
     @staticmethod
     def from_env(**overrides) -> "HipressConfig":
         cfg = HipressConfig()
+        hints = typing.get_type_hints(HipressConfig)
         for f in fields(HipressConfig):
             v = os.environ.get("HIPRESS_" + f.name.upper())
             if v is None:
                 continue
-            cur = getattr(cfg, f.name)
-            if isinstance(cur, bool):
-                setattr(cfg, f.name, v.lower() in ("1", "true", "yes"))
-            elif isinstance(cur, int):
+            # convert by the declared type (``int | None`` fields default to None, so
+            # the current value says nothing about them)
+            kinds = [t for t in typing.get_args(hints[f.name]) if t is not type(None)] or [hints[f.name]]
+            kind = kinds[0]
+            if kind is not str and v.strip().lower() in ("", "none") and type(None) in typing.get_args(hints[f.name]):
+                setattr(cfg, f.name, None)
+            elif kind is bool:
+                setattr(cfg, f.name, v.lower() in ("1", "true", "yes", "on"))
+            elif kind is int:
                 setattr(cfg, f.name, int(v))
-            elif isinstance(cur, float):
+            elif kind is float:
                 setattr(cfg, f.name, float(v))
             else:
                 setattr(cfg, f.name, v)

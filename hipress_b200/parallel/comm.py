@@ -184,8 +184,9 @@ def allreduce(tensor: torch.Tensor, average: bool = True, name: str | None = Non
             setattr(cfg, k, v)
         _syncers[key] = FlatSyncer(cfg)
     flat = out.reshape(-1).float().contiguous()
-    # a stable key: str hashes differ between processes and runs
-    _syncers[key].sync_(flat, key=zlib.crc32((name or "").encode()) % (1 << 20))
+    # a stable key (str hashes differ between processes and runs); the element count is
+    # part of it, so unnamed tensors of different sizes never share error-feedback state
+    _syncers[key].sync_(flat, key=zlib.crc32(f"{name or ''}#{flat.numel()}".encode()) % (1 << 20))
     if not average:
         flat.mul_(size())
     return flat.view_as(out).to(tensor.dtype)

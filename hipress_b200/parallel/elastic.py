@@ -22,23 +22,66 @@ from . import comm
 log = logging.getLogger("hipress")
 
 
+def _parse_set(text) -> set:
+    text = text.decode() if isinstance(text, bytes) else text
+    return {int(x) for x in text.split(",") if x != ""}
+
+
 def survivors_rendezvous(store, old_rank: int, old_world: int, dead, *, generation: int,
                          timeout_s: float = 30.0, prefix: str = "hipress"):
-    """Every survivor calls this with the same `dead` set (from PeerFailure.ranks) and
-    `generation` (a counter that grows with every recovery).  Returns (new_rank,
-    new_world): survivors keep their relative order."""
-    dead = set(dead)
-    alive = [r for r in range(old_world) if r not in dead]
-    if old_rank not in alive:
-        raise RuntimeError("a rank that was declared dead cannot rejoin")
+    """Every survivor calls this with the peers IT saw fail (PeerFailure.ranks) and the
+    same `generation` (a counter that grows with every recovery).  The survivors need
+    not have seen the same failures: each publishes its own set in the job's store, and
+    the membership everyone adopts is built from the union of the published sets --
+    a rank waits until every rank that is alive by the union has published, and
+    widens the union with whatever those ranks reported (two peers that fail close
+    together, or a departure one rank read from the store and another only noticed
+    as a missed heartbeat, no longer split the survivors).  The first rank to finish
+    records the result under ``final``; a rank that arrives at a different one adopts
+    the union and goes round again.  Returns (new_rank, new_world): survivors keep
+    their relative order."""
     key = f"{prefix}/gen{generation}"
-    store.add(f"{key}/joined", 1)
+    union = set(dead)
+    if old_rank in union:
+        raise RuntimeError("a rank that was declared dead cannot rejoin")
+    store.set(f"{key}/dead/{old_rank}", ",".join(map(str, sorted(union))))
     t0 = time.time()
-    while int(store.add(f"{key}/joined", 0)) < len(alive):
+    while True:
+        # widen the union with the reports of every rank that is alive by it
+        grew = True
+        missing = []
+        while grew:
+            grew = False
+            missing = []
+            for r in range(old_world):
+                if r in union or r == old_rank:
+                    continue
+                if store.check([f"{key}/dead/{r}"]):
+                    more = _parse_set(store.get(f"{key}/dead/{r}")) - union
+                    if more:
+                        union |= more
+                        grew = True
+                else:
+                    missing.append(r)
+        if old_rank in union:
+            raise RuntimeError(f"rank {old_rank} was declared dead by a peer and cannot rejoin")
+        if not missing:
+            mine = ",".join(map(str, sorted(union)))
+            agreed = store.compare_set(f"{key}/final", "", mine)
+            agreed = agreed.decode() if isinstance(agreed, bytes) else agreed
+            if agreed == mine:
+                break
+            other = _parse_set(agreed)
+            if other <= union:            # somebody finished with less: it will notice and come back
+                store.set(f"{key}/final", mine)
+                break
+            union |= other
+            continue
         if time.time() - t0 > timeout_s:
-            raise TimeoutError(f"only {int(store.add(key + '/joined', 0))} of {len(alive)} survivors "
-                               "reached the rendezvous")
+            raise TimeoutError(f"survivors {missing} never reached the rendezvous "
+                               f"(declared dead so far: {sorted(union)})")
         time.sleep(0.02)
+    alive = [r for r in range(old_world) if r not in union]
     return alive.index(old_rank), len(alive)
 
 

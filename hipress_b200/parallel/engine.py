@@ -204,10 +204,14 @@ class GradSyncEngine:
     def _make_entries(self, named):
         cfg = self.cfg
         plan = None
+        self.plan_source = "comp_threshold"     # what decided: reported by stats()
         if cfg.plan in ("auto", "auto:bucketed"):
             plan = self._auto_plan(named, bucketed=cfg.plan.endswith("bucketed"))
+            if plan is not None:
+                self.plan_source = f"{cfg.plan} ({self._plan_profile_name})"
         elif cfg.plan:
             plan = read_plan(cfg.plan)
+            self.plan_source = str(cfg.plan)
         entries = []
         for i, (name, p) in enumerate(named):
             n = p.numel()
@@ -239,6 +243,7 @@ class GradSyncEngine:
             log.info("no cost profile %s: falling back to comp_threshold", path)
             return None
         prof = CostProfile.from_json(path.read_text())
+        self._plan_profile_name = path.name
         if prof.nodes != self.N:
             log.warning("cost profile %s is for %d ranks, not %d: falling back to comp_threshold",
                         path, prof.nodes, self.N)
@@ -598,6 +603,11 @@ class GradSyncEngine:
                 if self.arena is not None:
                     self._poll_status()
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+            if self.arena is not None and self.cfg.strict_status:
+                # the host waits for this step's kernels and raises before the
+                # optimizer can apply a gradient that a late peer left incomplete
+                self._status_event.synchronize()
+                self._raise_on_status([w & 0xFFFFFFFF for w in self._status_host.tolist()])
         else:
             for b in self.buckets:
                 if not b.fused:
@@ -607,15 +617,23 @@ class GradSyncEngine:
         self.step_no += 1
         self._begin()
 
-    def _poll_status(self):
-        """Asynchronous read of the kernels' status words; a timeout recorded in
-        one step is raised at the next synchronize (or by check())."""
+    def _raise_on_status(self, words):
         from .fused import HipressTimeoutError, decode_status
+        if any(words):
+            self.status.zero_()
+            self._status_host.zero_()
+            raise HipressTimeoutError(f"rank {self.R}: " + decode_status(next(w for w in words if w)))
+
+    def _poll_status(self):
+        """Asynchronous read of the kernels' status words: a wait that expired in one
+        step is raised at the next synchronize, by check(), or -- with
+        ``strict_status`` -- by the same synchronize before the optimizer runs.  A CTA
+        whose wait expired writes neither error-feedback state nor gradient
+        (csrc/cuda/fused_dense.cu), so the late report costs one step whose affected
+        tensors carry the local instead of the averaged gradient, never corrupt
+        state; checkpoints call check() first."""
         if self._status_event is not None and self._status_event.query():
-            words = [w & 0xFFFFFFFF for w in self._status_host.tolist()]
-            if any(words):
-                self.status.zero_()
-                raise HipressTimeoutError(f"rank {self.R}: " + decode_status(words[0]))
+            self._raise_on_status([w & 0xFFFFFFFF for w in self._status_host.tolist()])
         self._status_host.copy_(self.status, non_blocking=True)
         self._status_event = torch.cuda.Event()
         self._status_event.record(self.comm_stream)
@@ -626,12 +644,8 @@ class GradSyncEngine:
         if self.arena is None:
             return
         self.arena.check_guards()
-        from .fused import HipressTimeoutError, decode_status
         torch.cuda.synchronize()
-        words = [w & 0xFFFFFFFF for w in self.status.cpu().tolist()]
-        if any(words):
-            self.status.zero_()
-            raise HipressTimeoutError(f"rank {self.R}: " + decode_status(words[0]))
+        self._raise_on_status([w & 0xFFFFFFFF for w in self.status.cpu().tolist()])
 
     # ------------------------------------------------------------ checkpoint
     def state_dict(self) -> dict:
@@ -697,15 +711,19 @@ class GradSyncEngine:
         tot = sum(e.numel for e in self.entries)
         return {"buckets": len(self.buckets), "fused_buckets": sum(b.fused for b in self.buckets),
                 "compressed_elems": comp_elems, "total_elems": tot, "backend": self.backend,
-                "kernel_launches": self.launch_count}
+                "kernel_launches": self.launch_count, "plan": self.plan_source,
+                "compressed_gradients": sum(1 for e in self.entries if e.compress and
+                                            self.backend != "allreduce")}
 
-    def close(self):
+    def close(self, collective: bool = True):
+        """``collective=False``: the process group this engine was built on is gone
+        (elastic recovery); release the symmetric memory without any barrier."""
         self.timeline.dump(self.R)
         for h in self._hooks:
             h.remove()
         self._hooks = []
         if self.arena is not None:
-            self.arena.close()
+            self.arena.close(collective=collective)
             self.arena = None
         if getattr(self, "_green", None):
             from .._native import lib as _lib

@@ -18,6 +18,8 @@ from ..ops.algorithms import AlgSpec
 from .simulate import chunk_elems
 
 TOPOLOGIES = {"ring": _lib.TOPO_RING, "ps": _lib.TOPO_PS}
+TRACE_PHASES = 20                    # HP_TRACE_PHASES / HP_TRACE_WORDS of capi.h
+TRACE_WORDS = 4 + 2 * TRACE_PHASES
 
 
 class HipressTimeoutError(RuntimeError):
@@ -27,10 +29,11 @@ class HipressTimeoutError(RuntimeError):
 def decode_status(word: int) -> str:
     if word == 0:
         return "ok"
-    phase = (word >> 16) & 0x7FFF
+    phase = (word >> 16) & 0x3FFF
     slot = (word >> 8) & 0xFF
     cta = word & 0xFF
-    return f"timeout phase={phase} slot={slot} cta={cta}"
+    what = "a peer gave up first (its input never arrived)" if word & 0x40000000 else "timeout"
+    return f"{what} phase={phase} slot={slot} cta={cta}"
 
 
 class FusedDenseBucket:
@@ -58,10 +61,9 @@ class FusedDenseBucket:
         _lib.check(L.hp_fused_dense_layout(self.topo, spec.alg, spec.bits, arr, len(self.sizes),
                                            nranks, C.byref(ib), C.byref(sb), C.byref(tt)), "layout")
         self.inbox_bytes, self.slot_bytes, self.tiles_total = ib.value, sb.value, tt.value
-        self.ctas = max(1, min(self.ctas, self.tiles_total))
-        self.flag_words = int(L.hp_fused_flag_words(self.topo, nranks, self.ctas))
+        phases = 2 * nranks + (1 if self.topo == _lib.TOPO_PS else 0)
+        self.ctas = max(1, min(self.ctas, self.tiles_total * phases))   # never more CTAs than work items
         self.inbox_ptrs = None
-        self.flag_ptrs = None
         self.status = None
         self._segs = (_lib.HpSeg * len(self.sizes))()
         self._comm = _lib.HpComm()
@@ -69,18 +71,17 @@ class FusedDenseBucket:
     # -- memory -----------------------------------------------------------
     def region_bytes(self) -> int:
         """Bytes this bucket needs in every rank's symmetric arena."""
-        return (self.inbox_bytes + 255) // 256 * 256 + (self.flag_words * 4 + 255) // 256 * 256
+        return (self.inbox_bytes + 255) // 256 * 256
 
     def bind(self, region_ptrs, status: torch.Tensor):
         """region_ptrs[q]: address of rank q's region for this bucket."""
-        ioff = (self.inbox_bytes + 255) // 256 * 256
         self.inbox_ptrs = [int(p) for p in region_ptrs]
-        self.flag_ptrs = [int(p) + ioff for p in region_ptrs]
         self.status = status
         if self.trace_enabled:
             nr = self.nranks if self.emulate else 1
-            self.trace = torch.zeros(4 * nr, dtype=torch.int64, device=status.device)
-            self._trace_init = torch.tensor([-1, 0, 0, 0] * nr, dtype=torch.int64, device=status.device)
+            self.trace = torch.zeros(TRACE_WORDS * nr, dtype=torch.int64, device=status.device)
+            self._trace_init = torch.tensor(([-1] + [0] * (TRACE_WORDS - 1)) * nr, dtype=torch.int64,
+                                            device=status.device)
         return self
 
     def bind_local(self, device):
@@ -94,6 +95,19 @@ class FusedDenseBucket:
 
     def chunk_elems(self, i: int) -> int:
         return chunk_elems(self.sizes[i], self.nranks)
+
+    def enable_trace(self, on: bool = True):
+        """Switch the device-side phase trace on or off for the following launches
+        (the bucket must be bound)."""
+        if not on:
+            self.trace = None
+            return
+        if self.trace is None:
+            nr = self.nranks if self.emulate else 1
+            dev = self.status.device
+            self.trace = torch.zeros(TRACE_WORDS * nr, dtype=torch.int64, device=dev)
+            self._trace_init = torch.tensor(([-1] + [0] * (TRACE_WORDS - 1)) * nr, dtype=torch.int64,
+                                            device=dev)
 
     # -- launch -----------------------------------------------------------
     def launch(self, grads, residuals=None, outs=None, server_residuals=None, *, step=0, salt=0,
@@ -115,12 +129,12 @@ class FusedDenseBucket:
                     if server_residuals is not None and server_residuals[i] is not None else None)
             s.n = self.sizes[i]
             s.id = tensor_ids[i] if tensor_ids is not None else i
-        self.epoch += 1
+        self.epoch = self.epoch % 0x7FFFFFFE + 1     # 31 bits: the top bit of the wire word is a mark
         cm.nranks, cm.rank, cm.emulate = self.nranks, self.rank, 1 if self.emulate else 0
         cm.epoch, cm.timeout_ns = self.epoch, self.timeout_ns
         for q in range(self.nranks):
             cm.inbox[q] = self.inbox_ptrs[q]
-            cm.flags[q] = self.flag_ptrs[q]
+            cm.flags[q] = None      # the dense kernels signal inside the payload slots
         cm.status = self.status.data_ptr()
         self._arm_trace(cm, stream)
         if self.emulate:
@@ -151,12 +165,12 @@ class FusedDenseBucket:
             s.g, s.r, s.out, s.sr = g_ptrs[i], r_ptrs[i], out_ptrs[i], sr_ptrs[i]
             s.n = self.sizes[i]
             s.id = tensor_ids[i] if tensor_ids is not None else i
-        self.epoch += 1
+        self.epoch = self.epoch % 0x7FFFFFFE + 1     # 31 bits: the top bit of the wire word is a mark
         cm.nranks, cm.rank, cm.emulate = self.nranks, self.rank, 0
         cm.epoch, cm.timeout_ns = self.epoch, self.timeout_ns
         for q in range(self.nranks):
             cm.inbox[q] = self.inbox_ptrs[q]
-            cm.flags[q] = self.flag_ptrs[q]
+            cm.flags[q] = None      # the dense kernels signal inside the payload slots
         cm.status = self.status.data_ptr()
         self._arm_trace(cm, stream)
         sp = self.spec
@@ -181,8 +195,24 @@ class FusedDenseBucket:
         (encode phases ms, whole kernel ms) from %globaltimer stamps."""
         if self.trace is None:
             return None
-        t = self.trace.cpu().view(-1, 4)
+        t = self.trace.cpu().view(-1, TRACE_WORDS)
         return [((int(r[1]) - int(r[0])) * 1e-6, (int(r[2]) - int(r[0])) * 1e-6) for r in t]
+
+    def last_trace_phases(self):
+        """Per rank played by the last launch: for every phase (ring: N hops then N
+        gathers; PS: N pushes, the server pass, N pulls) the time, in ms from the
+        first CTA's start, at which the last CTA finished it, and the mean time a CTA
+        spent polling for its input in that phase."""
+        if self.trace is None:
+            return None
+        phases = 2 * self.nranks + (1 if self.topo == _lib.TOPO_PS else 0)
+        out = []
+        for r in self.trace.cpu().view(-1, TRACE_WORDS):
+            t0 = int(r[0])
+            out.append([{"phase": p, "end_ms": (int(r[4 + p]) - t0) * 1e-6,
+                         "mean_poll_ms": int(r[4 + TRACE_PHASES + p]) * 1e-6 / self.ctas}
+                        for p in range(min(phases, TRACE_PHASES))])
+        return out
 
     def check_status(self):
         """Synchronising read of the status words; raises on a recorded timeout."""

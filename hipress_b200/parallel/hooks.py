@@ -55,7 +55,12 @@ class FlatSyncer:
             self.sched = HostSchedule(self.comp, self.cfg.topology, self.group)
         n = flat.numel()
         if n < self.cfg.comp_threshold or flat.dtype != torch.float32:
-            comm.allreduce_(flat)
+            # average over the ranks of THIS syncer's group (a sub-group, a DDP
+            # process_group), not over the whole job
+            N = comm.group_size(self.group)
+            if N > 1:
+                dist.all_reduce(flat, group=self.group)
+                flat.div_(N)
             return flat
         s, server, _ = self._state(key, n, flat.device)
         self.sched.sync([SegView(flat.view(-1), s, server, int(key) * 64)], step=self.step)

@@ -131,8 +131,8 @@ class DistributedOptimizer:
             for bo, _ in self._bucket_opts.values():
                 bo.state = self.optimizer.state
 
-    def close(self):
-        self.engine.close()
+    def close(self, collective: bool = True):
+        self.engine.close(collective=collective)
 
     def __getattr__(self, name):
         return getattr(self.__dict__["optimizer"], name)

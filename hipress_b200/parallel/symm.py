@@ -84,17 +84,23 @@ class SymmetricArena:
         if bad:
             raise RuntimeError(f"symmetric arena: regions {bad} were overrun (guard words changed)")
 
-    def close(self):
+    def close(self, collective: bool = True):
+        """Unmap the peers' arenas and free this rank's.  ``collective`` (the normal
+        shutdown): every rank of the group calls it, and barriers keep a rank from
+        freeing memory a peer's kernel may still store into.  ``collective=False`` is
+        for the survivors of a changed membership: the group the arena was built on
+        no longer exists, so no barrier can run; the caller guarantees that no kernel
+        of any surviving rank is in flight (recovery happens between steps)."""
         L = _lib.cuda()
         if self.local is None:
             return
         torch.cuda.synchronize()
-        if self.size > 1:
+        if collective and self.size > 1:
             dist.barrier(group=self.group)
         for p in self._opened:
             L.hp_cuda_ipc_close(p)
         self._opened = []
-        if self.size > 1:
+        if collective and self.size > 1:
             dist.barrier(group=self.group)
         L.hp_cuda_arena_free(self.local)
         self.local = None

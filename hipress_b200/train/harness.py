@@ -37,6 +37,10 @@ class Job:
     device: torch.device
     dtype: torch.dtype
 
+    def _net(self):
+        """The model itself (a DistributedDataParallel wrapper holds it as .module)."""
+        return getattr(self.model, "module", self.model)
+
     # ---------------------------------------------------------------- data
     def host_batch(self, seed: int):
         """One synthetic batch in pinned host memory."""
@@ -45,11 +49,11 @@ class Job:
             x = torch.randn(self.batch, 3, 224, 224, generator=g)
             y = torch.randint(0, 1000, (self.batch,), generator=g)
         elif self.kind == "lm":   # next-token targets over uniform random ids
-            V = self.model.vocab_size
+            V = self._net().vocab_size
             t = torch.randint(0, V, (self.batch, self.seq_len + 1), generator=g)
             x, y = t[:, :-1].contiguous(), t[:, 1:].contiguous()
         else:
-            V = self.model.c.vocab_size
+            V = self._net().c.vocab_size
             x = torch.randint(0, V, (self.batch, self.seq_len), generator=g)
             y = torch.full((self.batch, self.seq_len), -100, dtype=torch.long)
             mask = torch.rand(self.batch, self.seq_len, generator=g) < 0.15
@@ -202,7 +206,7 @@ class Job:
         from the new rank 0 so the replicas agree again."""
         old = self.optimizer
         inner, cfg = old.optimizer, old.config
-        old.close()
+        old.close(collective=False)   # the group its symmetric memory was built on is gone
         named = list(self.model.gluon_named_parameters()) if hasattr(self.model, "gluon_named_parameters") \
             else list(self.model.named_parameters())
         self.optimizer = DistributedOptimizer(inner, named, cfg)
@@ -250,3 +254,52 @@ def build_job(model_name: str = "vgg19", config: HipressConfig | None = None, *,
     opt = DistributedOptimizer(inner, named, cfg)
     broadcast_parameters(model.state_dict(), root_rank=0)
     return Job(model, opt, kind, batch or head["batch"], seq_len, device, dtype)
+
+
+class _PlainOptimizer:
+    """The face :class:`Job` expects of its optimizer, around a bare ``torch.optim``
+    optimizer (the baseline whose gradients DistributedDataParallel synchronises)."""
+    engine = None
+
+    def __init__(self, optimizer):
+        self.optimizer = optimizer
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.optimizer.zero_grad(set_to_none=set_to_none)
+
+    def step(self):
+        return self.optimizer.step()
+
+    def close(self):
+        pass
+
+
+def build_ddp_job(model_name: str = "vgg19", *, batch=None, seq_len: int = 128, dtype=torch.bfloat16,
+                  lr: float = 0.01, device=None, model_kwargs=None, seed: int = 0,
+                  bucket_cap_mb: int = 25) -> Job:
+    """The conventional uncompressed baseline: the same model, data shapes, precision
+    and optimizer under ``torch.nn.parallel.DistributedDataParallel`` (bucketed NCCL
+    all-reduce overlapped with backward, gradients as views of the buckets).  It stands
+    in for the reference's own uncompressed path ("the conventional PS and
+    Ring-allreduce ... PS-Lite and NCCL", README.md:153 of mark14wu/hipress), which
+    cannot be built here.  A lone process has no process group and runs the bare
+    model: with one rank DDP would add nothing but its bookkeeping."""
+    import torch.distributed as dist
+    if not comm.is_initialized():
+        comm.init()
+    name = model_name.lower().replace("-", "_")
+    head = HEADLINE.get(name, HEADLINE["vgg19"])
+    device = device or comm.device()
+    torch.manual_seed(seed)
+    model = get_model(name, **(model_kwargs or {})).to(device)
+    kind = "mlm" if name.startswith("bert") else ("lm" if name in ("lstm", "transformer") else "image")
+    if kind == "image" and device.type == "cuda":
+        model = model.to(memory_format=torch.channels_last)
+    model.train()
+    inner = torch.optim.SGD(model.parameters(), lr=lr, momentum=0.9,
+                            **({"fused": True} if device.type == "cuda" else {}))
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        model = DDP(model, device_ids=[device.index] if device.type == "cuda" else None,
+                    gradient_as_bucket_view=True, bucket_cap_mb=bucket_cap_mb)
+    return Job(model, _PlainOptimizer(inner), kind, batch or head["batch"], seq_len, device, dtype)

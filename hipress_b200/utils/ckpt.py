@@ -26,6 +26,10 @@ def save_checkpoint(directory, model, optimizer, *, epoch=0, step=0, extra=None)
     d = Path(directory)
     d.mkdir(parents=True, exist_ok=True)
     inner = getattr(optimizer, "optimizer", optimizer)
+    if getattr(optimizer, "engine", None) is not None:
+        # nothing is written while a device-side wait has expired or a region of the
+        # symmetric arena was overrun: raises HipressTimeoutError / RuntimeError
+        optimizer.engine.check()
     if comm.rank() == 0:
         tmp = d / "model.pt.tmp"
         torch.save({"model": model.state_dict(), "optimizer": inner.state_dict(), "epoch": epoch,

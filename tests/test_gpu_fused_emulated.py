@@ -127,3 +127,65 @@ def test_device_side_trace_reports_phase_times():
     # the stamps bracket the kernel itself: no longer than the event-timed launch
     assert total_ms <= ev0.elapsed_time(ev1) + 0.01
     assert int(b.trace[3]) == b.epoch
+
+
+@pytest.mark.parametrize("topology", ["ring", "ps"])
+def test_more_ctas_than_tiles_per_phase(topology):
+    """Work items rotate over the grid from phase to phase: with more CTAs than a
+    chunk has tiles, different hops run on different CTAs (and wait for one another
+    across the emulated ranks) and the result is still the simulated one."""
+    _run(topology, "tbq", {}, 4, [70001, 4096, 300, 1 << 17], steps=2, ctas=100)
+    _run(topology, "onebit", {}, 2, [9000], steps=2, ctas=20)
+
+
+def test_trace_splits_the_launch_into_phases():
+    c = Compressor("tbq")
+    N, n = 4, 1 << 20
+    b = FusedDenseBucket(c.spec, "ring", [n], N, 0, ctas=32, emulate=True, trace=True).bind_local("cuda")
+    G = torch.randn(N, n, device="cuda") * 0.02
+    Rr = torch.zeros(N, n, device="cuda")
+    b.launch([G], [Rr], [G])
+    torch.cuda.synchronize()
+    b.check_status()
+    per_rank = b.last_trace_phases()
+    assert len(per_rank) == N
+    for phases, (enc_ms, total_ms) in zip(per_rank, b.last_trace()):
+        assert len(phases) == 2 * N
+        ends = [p["end_ms"] for p in phases]
+        assert all(e > 0 for e in ends) and max(ends) <= total_ms + 1e-6
+        assert ends[N - 1] <= enc_ms + 1e-6          # the hops end before the gathers do
+        assert all(p["mean_poll_ms"] >= 0 for p in phases)
+
+
+def test_fused_kernel_gives_up_cleanly_when_a_peer_never_sends():
+    """Rank 0 of a two-rank ring whose peer does not exist: nothing ever fills the
+    slots it polls.  Every wait is bounded, so the launch ends by itself; the status
+    word names the wait; the sends of a CTA that gave up carry the mark that lets its
+    receivers give up at once; and neither the gradient nor the error-feedback state
+    of the chunks that needed the missing input is touched."""
+    import time
+    c = Compressor("tbq")
+    n = 20000
+    b = FusedDenseBucket(c.spec, "ring", [n], 2, 0, ctas=16, timeout_s=0.3)
+    arena = torch.zeros(2 * b.region_bytes(), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    b.bind([arena.data_ptr(), arena.data_ptr() + b.region_bytes()], status)
+    torch.manual_seed(5)
+    g = torch.randn(n, device="cuda") * 0.02
+    g0 = g.clone()
+    r = torch.zeros(n, device="cuda")
+    t0 = time.time()
+    b.launch_ptrs([g.data_ptr()], [r.data_ptr()], [g.data_ptr()], [None])
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    with pytest.raises(HipressTimeoutError):
+        b.check_status()
+    ch = chunk_elems(n, 2)
+    assert torch.equal(g, g0), "no averaged gradient is written from input that never arrived"
+    assert bool((r[:ch] != 0).any()), "hop 0 needs no input: its error feedback is kept"
+    assert bool((r[ch:] == 0).all()), "the hop that waited in vain leaves its state alone"
+    # the context is still usable and the bucket works again once the status is cleared
+    b1 = FusedDenseBucket(c.spec, "ring", [n], 1, 0, ctas=16).bind_local("cuda")
+    b1.launch([g], [torch.zeros_like(g)], [g])
+    torch.cuda.synchronize()
+    b1.check_status()

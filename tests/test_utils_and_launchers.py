@@ -326,3 +326,62 @@ def test_training_script_continues_after_a_rank_leaves(tmp_path):
     recs = [json.loads(r) for r in (tmp_path / "m0.jsonl").read_text().splitlines()]
     assert recs[-1]["step"] == 6 and recs[-1]["ranks"] == 2
     assert recs[-1]["loss"] == recs[-1]["loss"]
+
+
+def _split_view_worker(rank, world):
+    """Four ranks; ranks 2 and 3 leave at the same step.  Rank 0 only noticed rank 2,
+    rank 1 only rank 3: the rendezvous must still give both the same membership."""
+    from hipress_b200.parallel.elastic import survivors_rendezvous
+    from hipress_b200.utils.health import default_store
+    store = default_store()
+    if rank >= 2:
+        return {"left": True}
+    seen = [2] if rank == 0 else [3]
+    time.sleep(0.2 * rank)          # and they do not arrive together
+    return {"new": survivors_rendezvous(store, rank, world, seen, generation=1, timeout_s=10.0)}
+
+
+def test_survivors_agree_when_they_saw_different_failures():
+    res = spawn(_split_view_worker, 4)
+    assert res[0]["new"] == (0, 2) and res[1]["new"] == (1, 2)
+
+
+def test_environment_overrides_convert_by_declared_type(monkeypatch):
+    """Fields that default to None (bitwidth, plan) take their type from the
+    declaration, not from the current value."""
+    import hipress_b200 as hp
+    monkeypatch.setenv("HIPRESS_BITWIDTH", "2")
+    monkeypatch.setenv("HIPRESS_PLAN", "auto")
+    monkeypatch.setenv("HIPRESS_OVERLAP", "0")
+    monkeypatch.setenv("HIPRESS_RATIO", "0.01")
+    monkeypatch.setenv("HIPRESS_STRICT_STATUS", "true")
+    cfg = hp.HipressConfig.from_env()
+    assert cfg.bitwidth == 2 and isinstance(cfg.bitwidth, int)
+    assert cfg.plan == "auto" and cfg.overlap is False and cfg.ratio == 0.01 and cfg.strict_status is True
+    spec = hp.get_algorithm("terngrad", **cfg.algorithm_kwargs())
+    assert spec.bits == 2
+    monkeypatch.setenv("HIPRESS_BITWIDTH", "none")
+    assert hp.HipressConfig.from_env().bitwidth is None
+
+
+def _subgroup_worker(rank, world):
+    """FlatSyncer on a 2-of-4 sub-group: small (uncompressed) tensors are averaged
+    over the sub-group only."""
+    import torch.distributed as dist
+    import hipress_b200 as hp
+    from hipress_b200.parallel.hooks import FlatSyncer
+    groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+    g = groups[rank // 2]
+    fs = FlatSyncer(hp.HipressConfig(algorithm="tbq", comp_threshold=1000), group=g)
+    small = torch.full((10,), float(rank))
+    fs.sync_(small, key=0)
+    a = hp.allreduce(torch.full((2000,), 0.02), algorithm="tbq", threshold=0.01)
+    b = hp.allreduce(torch.full((3000,), 0.02), algorithm="tbq", threshold=0.01)   # unnamed, other size
+    return {"small": small, "a": a, "b": b}
+
+
+def test_flat_syncer_respects_its_group_and_unnamed_tensors_do_not_share_state():
+    res = spawn(_subgroup_worker, 4)
+    for r in range(4):
+        assert torch.allclose(res[r]["small"], torch.full((10,), 0.5 if r < 2 else 2.5))
+        assert res[r]["a"].shape == (2000,) and res[r]["b"].shape == (3000,)
