@@ -156,12 +156,12 @@ int hp_cpu_dense_encode(int alg, int bits, const float* g, float* r,
       meta[2 * t] = mn;
       meta[2 * t + 1] = mx;
       const float gap = tern_gap(mn, mx, bits);
-      const float inv_gap = tern_inv_gap(gap);
+      const float scale16 = tern_scale16(gap);
       for (uint64_t i = 0; i < m; ++i) {
         const uint64_t ge = elem_offset + t0 + i;
         Philox4 rnd = philox4x32(rnd16_counter(ge), tensor_id, step, salt,
                                     (uint32_t)seed, (uint32_t)(seed >> 32));
-        uint32_t c = tern_code(x[i], mn, inv_gap, u01_16(rnd.v[ge & 3], rnd16_half(ge)), bits);
+        uint32_t c = tern_code(x[i], mn, scale16, rnd16(rnd.v[ge & 3], rnd16_half(ge)), bits);
         put_code(codes, t0 + i, bits, c);
         if (r) r[t0 + i] = x[i] - tern_value(c, mn, gap);
       }

@@ -193,10 +193,10 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
     meta[0] = mn;
     meta[1] = mx;
   }
-  float gap = 0.0f, inv_gap = 0.0f;
+  float gap = 0.0f, scale16 = 0.0f;
   if (ALG == kTernGrad) {
     gap = tern_gap(meta[0], meta[1], B);
-    inv_gap = tern_inv_gap(gap);
+    scale16 = tern_scale16(gap);
   }
   // TernGrad: one Philox call per pair of rows (see rnd16_counter); a tile that does
   // not start on a 2048-element boundary of its tensor cannot share calls
@@ -225,7 +225,7 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
           c = tbq_code(x[j][e], P.tau);
           d = tbq_value(c, P.tau);
         } else {
-          c = tern_code(x[j][e], meta[0], inv_gap, u01_16(rnd.v[e], half), B);
+          c = tern_code(x[j][e], meta[0], scale16, rnd16(rnd.v[e], half), B);
           d = ERR ? tern_value(c, meta[0], gap) : 0.0f;
         }
         f |= c << (e * B);

@@ -101,8 +101,7 @@ __device__ __forceinline__ uint2 ll_load(const uint2* slot) {
 // wait expired keeps sending (so nobody downstream has to wait out a timeout of
 // its own) but marks what it sends, and a receiver that sees the mark gives up at
 // once as well.  A CTA that has given up ("poisoned") touches neither the error
-// feedback state nor the gradient any more.
-constexpr uint32_t kGaveUp = 0x80000000u;
+// feedback state nor the gradient any more.  (kGaveUp: sync.cuh)
 
 __device__ __forceinline__ uint32_t ll_finish(const uint2* slot, uint2 v, const HpComm& cm,
                                               uint32_t* status, uint32_t code, WaitState& ws) {

@@ -1,5 +1,8 @@
-// Fused CaSync-PS for the top-k algorithms (DGC, GradDrop): a short, fixed
-// sequence of launches per bucket with no NCCL call and no host round trip.
+// Fused CaSync-PS and CaSync-Ring for the top-k algorithms (DGC, GradDrop): ONE
+// persistent cooperative launch per bucket, no NCCL call, no host round trip.  The
+// stages below run as grid-synchronised phases of that launch (a bounded barrier
+// over the launch's own CTAs between phases that depend on one another); waiting
+// across GPUs happens on release / acquire flags, as in the dense kernels.
 //
 //   push   : per (tensor, owner) unit: state update + radix select (3 histogram
 //            passes) + compaction whose (index, value) pairs are stored straight
@@ -12,9 +15,10 @@
 //   pull   : every rank zero-fills the gradient, waits for each owner's flag and
 //            scatters value / N.
 //
-// All units of a bucket are batched in each launch (gridDim.y = units), which is
-// the "bulk synchronisation" of many small tensors.  Waiting only happens across
-// GPUs: the launches of one GPU are ordered by the stream.
+// All units of a bucket are batched in every phase (the CTAs share out the units'
+// slices), which is the "bulk synchronisation" of many small tensors.  An earlier
+// version ran every stage as a launch of its own: 19 launches per bucket for PS and
+// 9 per ring hop, with a floor of about 0.2 ms per bucket from launch latency alone.
 //
 // Reference parity: DGC through the PS topology is the reference's ResNet-50
 // style configuration (--comp_alg dgc, README.md:180; CaSync-PS cost shape
@@ -61,24 +65,90 @@ __device__ __forceinline__ void write_empty_header(uint8_t* out, int alg) {
   *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(&h);
 }
 
+// ------------------------------------------------------ persistent-kernel plumbing
+struct SpSmem {
+  uint32_t sh[kBins];
+  FindSmem fs;
+  EmitSmem es;
+  SplitSmem sp;
+  WaitState wst;
+  uint32_t any;
+};
+
+// control words of one rank played by a launch, behind its histogram blocks; zero
+// when the kernel starts (cleared with the histograms)
+constexpr int kCtlBarrier = 0;
+constexpr int kCtlWords = 16;
+
+struct SpCtx {
+  int N, R, E;
+  uint32_t G;            // CTAs that play this rank
+  uint32_t* ws;          // histogram / counter blocks of this rank, kWsWords per unit
+  uint8_t* cand;         // candidate lists of this rank
+  uint32_t* ctl;         // control words of this rank
+  uint32_t* status;
+  uint32_t gen;          // barriers passed so far
+};
+
+// the flag value a CTA releases: its epoch, marked when it had given up on a wait
+__device__ __forceinline__ uint32_t flag_value(const HpComm& cm, const SpSmem& sm) {
+  return cm.epoch | (*(volatile const int*)&sm.wst.poisoned ? kGaveUp : 0u);
+}
+
+__device__ __forceinline__ void sp_barrier(const HpComm& cm, SpCtx& cx, SpSmem& sm) {
+  // a peer may be late by up to one wait bound before a CTA reaches the barrier
+  grid_barrier(cx.ctl + kCtlBarrier, cx.gen, cx.G, 2 * cm.timeout_ns + 1000000000ull, cx.status,
+               HP_STATUS_TIMEOUT | (8u << 16) | (cx.gen & 255u), sm.wst);
+}
+
+// Phase driver: `units` work units, each cut into `per` slices; slice v of the phase
+// goes to CTA v % G.  f(unit, slice, per) is what one CTA of the old one-launch-per-
+// stage grid did.
+template <typename F>
+__device__ __forceinline__ void run_units(const SpCtx& cx, uint32_t units, uint32_t per, F f) {
+  const uint32_t total = units * per;
+  for (uint32_t v = blockIdx.x; v < total; v += cx.G) {
+    f((int)(v / per), v % per, per);
+    __syncthreads();  // shared memory is reused by the next slice
+  }
+}
+
+// did any of `units` units (histogram blocks from `ws`) overflow its candidate list?
+// Read after a barrier that follows every writer, so all CTAs agree.
+__device__ __forceinline__ bool any_overflow(const uint32_t* ws, uint32_t units, SpSmem& sm) {
+  if (threadIdx.x == 0) sm.any = 0;
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < units; i += kSpThreads)
+    if (__ldcg(ws + (size_t)i * kWsWords + kWsOverflow)) sm.any = 1;
+  __syncthreads();
+  const bool r = sm.any != 0;
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ uint32_t slices_heavy(const SpCtx& cx, uint32_t units) {
+  const uint32_t p = cx.G / (units ? units : 1);
+  return p < 1 ? 1 : (p > 592 ? 592 : p);
+}
+__device__ __forceinline__ uint32_t slices_cap(const SpCtx& cx, uint32_t units, uint32_t cap) {
+  const uint32_t p = slices_heavy(cx, units);
+  return p > cap ? cap : p;
+}
+
 // ---------------------------------------------------------------- push
 // unit y = seg * N + owner
 // STAGE 0: update + hist0   1: split (certain elements go to the owner at once)
 //       2,3: digit passes on the candidate list   4: candidate compaction + flag
 //       5,6,7: full-array passes and compaction, only after a candidate overflow
 template <int STAGE>
-__global__ void __launch_bounds__(kSpThreads)
-sp_push_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_all,
-               uint8_t* cand_all) {
-  __shared__ uint32_t sh[kBins];
-  __shared__ FindSmem fs;
-  __shared__ EmitSmem es;
-  const int N = cm.nranks;
-  const int si = blockIdx.y / N, c = blockIdx.y % N;
+__device__ __forceinline__ void push_stage(const SpBucket& bk, const HpComm& cm, const SpCtx& cx,
+                                           SpSmem& sm, int y, uint32_t x, uint32_t nx) {
+  const int N = cx.N, R = cx.R, E = cx.E;
+  const int si = y / N, c = y % N;
   const SpSeg& sg = bk.seg[si];
   const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, c);
-  uint32_t* ws = ws_all + (size_t)blockIdx.y * kWsWords;
-  float* cand_val = reinterpret_cast<float*>(cand_all + (sg.cand_push + (uint64_t)c * sg.cap) * 8);
+  uint32_t* ws = cx.ws + (size_t)y * kWsWords;
+  float* cand_val = reinterpret_cast<float*>(cx.cand + (sg.cand_push + (uint64_t)c * sg.cap) * 8);
   uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + sg.cap);
   const size_t off = (size_t)c * sg.chunk;
   const float* g = sg.g + E * cm.emu_stride_g + off;
@@ -92,40 +162,40 @@ sp_push_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_al
   bool last = false;
   if (STAGE == 0) {
     if (len == 0) return;
-    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
-    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
+    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
+    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
     return;
   } else if (STAGE == 1) {
     if (len == 0) return;
-    __shared__ SplitSmem sp;
-    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, sp, blockIdx.x, gridDim.x);
+    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, sm.fs, sm.sp, x, nx);
     return;
   } else if (STAGE == 2 || STAGE == 3) {
     if (len == 0 || ws[kWsOverflow]) return;
-    if (STAGE == 2) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
-    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    if (STAGE == 2) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sm.sh, sm.fs, x, nx);
+    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sm.sh, sm.fs, x, nx);
     return;
   } else if (STAGE == 4) {
     if (len == 0) {
-      last = blockIdx.x == 0 && threadIdx.x == 0;
+      last = x == 0 && threadIdx.x == 0;
       if (last) write_empty_header(dst, bk.alg);
     } else {
       if (ws[kWsOverflow]) return;
-      last = emit_body(bk.alg, cand_val, u, ws[kWsCandCount], k, sg.kmax, d, ws, fs, es, blockIdx.x,
-                       gridDim.x, cand_idx, a, len);
+      last = emit_body(bk.alg, cand_val, u, ws[kWsCandCount], k, sg.kmax, d, ws, sm.fs, sm.es, x, nx,
+                       cand_idx, a, len);
     }
   } else if (STAGE == 5 || STAGE == 6) {
     if (len == 0 || !ws[kWsOverflow]) return;
-    if (STAGE == 5) pass_body<1>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
-    else pass_body<2>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    if (STAGE == 5) pass_body<1>(a, len, k, ws, sm.sh, sm.fs, x, nx);
+    else pass_body<2>(a, len, k, ws, sm.sh, sm.fs, x, nx);
     return;
   } else {
     if (len == 0 || !ws[kWsOverflow]) return;
-    last = emit_body(bk.alg, a, u, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+    last = emit_body(bk.alg, a, u, len, k, sg.kmax, d, ws, sm.fs, sm.es, x, nx);
   }
-  if (last) {  // thread 0 of the CTA that completed the unit
+  if (last) {  // thread 0 of the slice that completed the unit
     __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[c]) + (size_t)R * bk.nseg + si, cm.epoch);
+    st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[c]) + (size_t)R * bk.nseg + si,
+                   flag_value(cm, sm));
   }
 }
 
@@ -134,22 +204,16 @@ sp_push_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_al
 // STAGE 0: wait + scatter-add   1: hist0   2: split (to every rank)   3,4: candidate
 //       digit passes   5: candidate compaction + flags   6,7,8: overflow path
 template <int STAGE>
-__global__ void __launch_bounds__(kSpThreads)
-sp_server_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_all,
-                 uint8_t* cand_all) {
-  __shared__ uint32_t sh[kBins];
-  __shared__ FindSmem fs;
-  __shared__ EmitSmem es;
-  __shared__ WaitState wst;
-  const int N = cm.nranks;
-  const int si = blockIdx.y;
+__device__ __forceinline__ void server_stage(const SpBucket& bk, const HpComm& cm, const SpCtx& cx,
+                                             SpSmem& sm, int y, uint32_t x, uint32_t nx) {
+  const int N = cx.N, R = cx.R, E = cx.E;
+  const int si = y;
   const SpSeg& sg = bk.seg[si];
   const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, R);
-  uint32_t* ws = ws_all + (size_t)blockIdx.y * kWsWords;
-  float* cand_val = reinterpret_cast<float*>(cand_all + sg.cand_srv * 8);
+  uint32_t* ws = cx.ws + ((size_t)bk.nseg * N + y) * kWsWords;
+  float* cand_val = reinterpret_cast<float*>(cx.cand + sg.cand_srv * 8);
   uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + sg.cap);
   float* acc = sg.sr + E * cm.emu_stride_sr;
-  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   const uint32_t k = (uint32_t)sparse_k(len, bk.ratio);
   EmitDst d;
   d.n = N;
@@ -158,89 +222,85 @@ sp_server_kernel(const SpBucket bk, const HpComm cm, int R, int E, uint32_t* ws_
                sg.pay_off;
   bool last = false;
   if (STAGE == 0) {
-    wait_init(wst);
     const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(cm.flags[R]);
     for (int q = 0; q < N; ++q)
-      wait_flag(my_flags + (size_t)q * bk.nseg + si, cm.epoch, cm.timeout_ns, status,
-                HP_STATUS_TIMEOUT | (4u << 16) | ((uint32_t)q << 8) | (si & 255), wst);
+      wait_flag(my_flags + (size_t)q * bk.nseg + si, cm.epoch, cm.timeout_ns, cx.status,
+                HP_STATUS_TIMEOUT | (4u << 16) | ((uint32_t)q << 8) | (si & 255), sm.wst);
     if (len == 0) return;
     const uint8_t* inbox = reinterpret_cast<const uint8_t*>(cm.inbox[R]);
     for (int q = 0; q < N; ++q)
-      scatter_body(inbox + (size_t)q * bk.slot_bytes + sg.pay_off, acc, len, sg.kmax, 1.0f, 2,
-                   blockIdx.x, gridDim.x);
+      scatter_body(inbox + (size_t)q * bk.slot_bytes + sg.pay_off, acc, len, sg.kmax, 1.0f, 2, x, nx);
     return;
   } else if (STAGE == 1) {
     if (len == 0) return;
-    pass0_body<0>(nullptr, acc, nullptr, len, 0.0f, ws, sh, blockIdx.x, gridDim.x);
+    pass0_body<0>(nullptr, acc, nullptr, len, 0.0f, ws, sm.sh, x, nx);
     return;
   } else if (STAGE == 2) {
     if (len == 0) return;
-    __shared__ SplitSmem sp;
-    split_body(acc, nullptr, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, sp, blockIdx.x,
-               gridDim.x);
+    split_body(acc, nullptr, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, sm.fs, sm.sp, x, nx);
     return;
   } else if (STAGE == 3 || STAGE == 4) {
     if (len == 0 || ws[kWsOverflow]) return;
-    if (STAGE == 3) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
-    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    if (STAGE == 3) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sm.sh, sm.fs, x, nx);
+    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sm.sh, sm.fs, x, nx);
     return;
   } else if (STAGE == 5) {
     if (len == 0) {
-      last = blockIdx.x == 0 && threadIdx.x == 0;
+      last = x == 0 && threadIdx.x == 0;
       if (last)
         for (int q = 0; q < N; ++q) write_empty_header(d.out[q], bk.alg);
     } else {
       if (ws[kWsOverflow]) return;
-      last = emit_body(bk.alg, cand_val, nullptr, ws[kWsCandCount], k, sg.kmax, d, ws, fs, es,
-                       blockIdx.x, gridDim.x, cand_idx, acc, len);
+      last = emit_body(bk.alg, cand_val, nullptr, ws[kWsCandCount], k, sg.kmax, d, ws, sm.fs, sm.es, x,
+                       nx, cand_idx, acc, len);
     }
   } else if (STAGE == 6 || STAGE == 7) {
     if (len == 0 || !ws[kWsOverflow]) return;
-    if (STAGE == 6) pass_body<1>(acc, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
-    else pass_body<2>(acc, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    if (STAGE == 6) pass_body<1>(acc, len, k, ws, sm.sh, sm.fs, x, nx);
+    else pass_body<2>(acc, len, k, ws, sm.sh, sm.fs, x, nx);
     return;
   } else {
     if (len == 0 || !ws[kWsOverflow]) return;
-    last = emit_body(bk.alg, acc, nullptr, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+    last = emit_body(bk.alg, acc, nullptr, len, k, sg.kmax, d, ws, sm.fs, sm.es, x, nx);
   }
   if (last) {
     __threadfence_system();
+    const uint32_t fv = flag_value(cm, sm);
     for (int q = 0; q < N; ++q)
       st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + q) % N]) +
                          (size_t)(N + R) * bk.nseg + si,
-                     cm.epoch);
+                     fv);
   }
 }
 
 // ---------------------------------------------------------------- pull
-// STAGE 0: zero-fill (unit y = seg); STAGE 1: wait + scatter (unit y = seg * N + owner)
-template <int STAGE>
-__global__ void __launch_bounds__(kSpThreads)
-sp_pull_kernel(const SpBucket bk, const HpComm cm, int R, int E) {
-  __shared__ WaitState wst;
-  const int N = cm.nranks;
-  if (STAGE == 0) {
-    const SpSeg& sg = bk.seg[blockIdx.y];
-    float* out = sg.out + E * cm.emu_stride_out;
-    const bool vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-    const uint64_t stride = (uint64_t)gridDim.x * kSpThreads * 4;
-    for (uint64_t i = ((uint64_t)blockIdx.x * kSpThreads + threadIdx.x) * 4; i < sg.n; i += stride)
-      st4(out, i, sg.n, vec, make_float4(0.f, 0.f, 0.f, 0.f));
-    return;
-  }
-  const int si = blockIdx.y / N, j = blockIdx.y % N;
+// zero-fill of the result (unit y = seg)
+__device__ __forceinline__ void zero_stage(const SpBucket& bk, const HpComm& cm, const SpCtx& cx,
+                                           int y, uint32_t x, uint32_t nx) {
+  const SpSeg& sg = bk.seg[y];
+  float* out = sg.out + cx.E * cm.emu_stride_out;
+  const bool vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const uint64_t stride = (uint64_t)nx * kSpThreads * 4;
+  for (uint64_t i = ((uint64_t)x * kSpThreads + threadIdx.x) * 4; i < sg.n; i += stride)
+    st4(out, i, sg.n, vec, make_float4(0.f, 0.f, 0.f, 0.f));
+}
+
+// wait for the reduced chunk c that arrives in inbox slot `slot` and scatter value / N
+// into the (zero-filled) result; unit y = seg * N + j.  A CTA that has given up leaves
+// the result alone.
+__device__ __forceinline__ void gather_stage(const SpBucket& bk, const HpComm& cm, const SpCtx& cx,
+                                             SpSmem& sm, int si, int slot, int c, uint32_t phase,
+                                             uint32_t x, uint32_t nx) {
   const SpSeg& sg = bk.seg[si];
-  const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, j);
-  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
-  wait_init(wst);
-  wait_flag(reinterpret_cast<const uint32_t*>(cm.flags[R]) + (size_t)(N + j) * bk.nseg + si, cm.epoch,
-            cm.timeout_ns, status, HP_STATUS_TIMEOUT | (5u << 16) | ((uint32_t)j << 8) | (si & 255),
-            wst);
-  if (len == 0) return;
-  const uint8_t* p = reinterpret_cast<const uint8_t*>(cm.inbox[R]) + (size_t)(N + j) * bk.slot_bytes +
+  const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, c);
+  wait_flag(reinterpret_cast<const uint32_t*>(cm.flags[cx.R]) + (size_t)slot * bk.nseg + si, cm.epoch,
+            cm.timeout_ns, cx.status,
+            HP_STATUS_TIMEOUT | (phase << 16) | ((uint32_t)(slot & 255) << 8) | (si & 255), sm.wst);
+  if (len == 0 || *(volatile int*)&sm.wst.poisoned) return;
+  const uint8_t* p = reinterpret_cast<const uint8_t*>(cm.inbox[cx.R]) + (size_t)slot * bk.slot_bytes +
                      sg.pay_off;
-  scatter_body(p, sg.out + E * cm.emu_stride_out + (size_t)j * sg.chunk, len, sg.kmax, bk.inv_n, 0,
-               blockIdx.x, gridDim.x);
+  scatter_body(p, sg.out + cx.E * cm.emu_stride_out + (size_t)c * sg.chunk, len, sg.kmax, bk.inv_n, 0,
+               x, nx);
 }
 
 // ---------------------------------------------------------------- ring
@@ -252,27 +312,21 @@ sp_pull_kernel(const SpBucket bk, const HpComm cm, int R, int E) {
 // STAGE 0: wait + add incoming   1: update + hist0   2: split   3,4: candidate digit
 //       passes   5: candidate compaction + flag(s)   6,7,8: overflow path
 template <int STAGE>
-__global__ void __launch_bounds__(kSpThreads)
-sp_ring_kernel(const SpBucket bk, const HpComm cm, int R, int E, int hop, uint32_t* ws_all,
-               uint8_t* cand_all) {
-  __shared__ uint32_t sh[kBins];
-  __shared__ FindSmem fs;
-  __shared__ EmitSmem es;
-  __shared__ WaitState wst;
-  const int N = cm.nranks;
-  const int si = blockIdx.y;
+__device__ __forceinline__ void ring_stage(const SpBucket& bk, const HpComm& cm, const SpCtx& cx,
+                                           SpSmem& sm, int hop, int y, uint32_t x, uint32_t nx) {
+  const int N = cx.N, R = cx.R, E = cx.E;
+  const int si = y;
   const int c = (R - hop + N) % N;
   const bool last_hop = hop == N - 1;
   const SpSeg& sg = bk.seg[si];
   const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, c);
-  uint32_t* ws = ws_all + ((size_t)hop * bk.nseg + si) * kWsWords;
-  float* cand_val = reinterpret_cast<float*>(cand_all + (sg.cand_push + (uint64_t)c * sg.cap) * 8);
+  uint32_t* ws = cx.ws + ((size_t)hop * bk.nseg + si) * kWsWords;
+  float* cand_val = reinterpret_cast<float*>(cx.cand + (sg.cand_push + (uint64_t)c * sg.cap) * 8);
   uint32_t* cand_idx = reinterpret_cast<uint32_t*>(cand_val + sg.cap);
   const size_t off = (size_t)c * sg.chunk;
   const float* g = sg.g + E * cm.emu_stride_g + off;
   float* a = sg.a + E * cm.emu_stride_r + off;
   float* u = sg.u ? sg.u + E * cm.emu_stride_r + off : nullptr;
-  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
   const uint32_t k = (uint32_t)sparse_k(len, bk.ratio);
   EmitDst d;
   if (!last_hop) {
@@ -287,82 +341,189 @@ sp_ring_kernel(const SpBucket bk, const HpComm cm, int R, int E, int hop, uint32
   bool last = false;
   if (STAGE == 0) {
     if (hop == 0) return;
-    wait_init(wst);
     wait_flag(reinterpret_cast<const uint32_t*>(cm.flags[R]) + (size_t)(hop - 1) * bk.nseg + si,
-              cm.epoch, cm.timeout_ns, status,
-              HP_STATUS_TIMEOUT | (6u << 16) | ((uint32_t)(hop - 1) << 8) | (si & 255), wst);
+              cm.epoch, cm.timeout_ns, cx.status,
+              HP_STATUS_TIMEOUT | (6u << 16) | ((uint32_t)(hop - 1) << 8) | (si & 255), sm.wst);
     if (len == 0) return;
     scatter_body(reinterpret_cast<const uint8_t*>(cm.inbox[R]) + (size_t)(hop - 1) * bk.slot_bytes +
                      sg.pay_off,
-                 a, len, sg.kmax, 1.0f, 1, blockIdx.x, gridDim.x);
+                 a, len, sg.kmax, 1.0f, 1, x, nx);
     return;
   } else if (STAGE == 1) {
     if (len == 0) return;
-    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
-    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sh, blockIdx.x, gridDim.x);
+    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
+    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
     return;
   } else if (STAGE == 2) {
     if (len == 0) return;
-    __shared__ SplitSmem sp;
-    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, fs, sp, blockIdx.x, gridDim.x);
+    split_body(a, u, len, k, sg.kmax, d, ws, cand_val, cand_idx, sg.cap, sm.fs, sm.sp, x, nx);
     return;
   } else if (STAGE == 3 || STAGE == 4) {
     if (len == 0 || ws[kWsOverflow]) return;
-    if (STAGE == 3) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
-    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sh, fs, blockIdx.x, gridDim.x);
+    if (STAGE == 3) pass_body<1>(cand_val, ws[kWsCandCount], k, ws, sm.sh, sm.fs, x, nx);
+    else pass_body<2>(cand_val, ws[kWsCandCount], k, ws, sm.sh, sm.fs, x, nx);
     return;
   } else if (STAGE == 5) {
     if (len == 0) {
-      last = blockIdx.x == 0 && threadIdx.x == 0;
+      last = x == 0 && threadIdx.x == 0;
       if (last)
         for (int q = 0; q < d.n; ++q) write_empty_header(d.out[q], bk.alg);
     } else {
       if (ws[kWsOverflow]) return;
-      last = emit_body(bk.alg, cand_val, u, ws[kWsCandCount], k, sg.kmax, d, ws, fs, es, blockIdx.x,
-                       gridDim.x, cand_idx, a, len);
+      last = emit_body(bk.alg, cand_val, u, ws[kWsCandCount], k, sg.kmax, d, ws, sm.fs, sm.es, x, nx,
+                       cand_idx, a, len);
     }
   } else if (STAGE == 6 || STAGE == 7) {
     if (len == 0 || !ws[kWsOverflow]) return;
-    if (STAGE == 6) pass_body<1>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
-    else pass_body<2>(a, len, k, ws, sh, fs, blockIdx.x, gridDim.x);
+    if (STAGE == 6) pass_body<1>(a, len, k, ws, sm.sh, sm.fs, x, nx);
+    else pass_body<2>(a, len, k, ws, sm.sh, sm.fs, x, nx);
     return;
   } else {
     if (len == 0 || !ws[kWsOverflow]) return;
-    last = emit_body(bk.alg, a, u, len, k, sg.kmax, d, ws, fs, es, blockIdx.x, gridDim.x);
+    last = emit_body(bk.alg, a, u, len, k, sg.kmax, d, ws, sm.fs, sm.es, x, nx);
   }
   if (last) {
     __threadfence_system();
+    const uint32_t fv = flag_value(cm, sm);
     if (!last_hop) {
-      st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + 1) % N]) + (size_t)hop * bk.nseg + si,
-                     cm.epoch);
+      st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + 1) % N]) + (size_t)hop * bk.nseg + si, fv);
     } else {
       for (int q = 0; q < N; ++q)
         st_release_sys(reinterpret_cast<uint32_t*>(cm.flags[(R + q) % N]) +
                            (size_t)(N - 1 + R) * bk.nseg + si,
-                       cm.epoch);
+                       fv);
     }
   }
 }
 
-// gather of the ring: unit y = seg * N + src; rank src finalised chunk src + 1
-__global__ void __launch_bounds__(kSpThreads)
-sp_ring_gather_kernel(const SpBucket bk, const HpComm cm, int R, int E) {
-  __shared__ WaitState wst;
-  const int N = cm.nranks;
-  const int si = blockIdx.y / N, src = blockIdx.y % N;
-  const int c = (src + 1) % N;
-  const SpSeg& sg = bk.seg[si];
-  const uint32_t len = sp_chunk_valid(sg.n, sg.chunk, c);
-  uint32_t* status = reinterpret_cast<uint32_t*>(cm.status) + 4 * E;
-  wait_init(wst);
-  wait_flag(reinterpret_cast<const uint32_t*>(cm.flags[R]) + (size_t)(N - 1 + src) * bk.nseg + si,
-            cm.epoch, cm.timeout_ns, status,
-            HP_STATUS_TIMEOUT | (7u << 16) | ((uint32_t)src << 8) | (si & 255), wst);
-  if (len == 0) return;
-  const uint8_t* p = reinterpret_cast<const uint8_t*>(cm.inbox[R]) +
-                     (size_t)(N - 1 + src) * bk.slot_bytes + sg.pay_off;
-  scatter_body(p, sg.out + E * cm.emu_stride_out + (size_t)c * sg.chunk, len, sg.kmax, bk.inv_n, 0,
-               blockIdx.x, gridDim.x);
+// ------------------------------------------------------------- the two kernels
+struct SpLaunch {
+  uint8_t* ws;            // scratch of all ranks played by the launch
+  uint64_t ws_rank_bytes; // per rank: histogram blocks, control words, candidate lists
+  uint64_t hist_words;    // histogram words per rank (the control words follow)
+  uint64_t hist_bytes;    // offset of the candidate lists inside a rank's scratch
+};
+
+__device__ __forceinline__ void sp_prologue(const HpComm& cm, const SpLaunch& L, SpCtx& cx,
+                                            SpSmem& sm) {
+  cx.N = cm.nranks;
+  cx.R = cm.emulate ? (int)blockIdx.y : cm.rank;
+  cx.E = cm.emulate ? (int)blockIdx.y : 0;
+  cx.G = gridDim.x;
+  uint8_t* base = L.ws + (size_t)cx.E * L.ws_rank_bytes;
+  cx.ws = reinterpret_cast<uint32_t*>(base);
+  cx.ctl = cx.ws + L.hist_words;
+  cx.cand = base + L.hist_bytes;
+  cx.status = reinterpret_cast<uint32_t*>(cm.status) + 4 * cx.E;
+  cx.gen = 0;
+  wait_init(sm.wst);
+}
+
+// PS: push (every rank selects per owner and stores the pairs into the owner's
+// inbox), server (the owner adds the N payloads, re-selects, stores the result into
+// every inbox), pull (every rank scatters value / N).  11 barriers when no candidate
+// list overflows.
+__global__ void __launch_bounds__(kSpThreads, 3)
+sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
+  __shared__ SpSmem sm;
+  SpCtx cx;
+  sp_prologue(cm, L, cx, sm);
+  const uint32_t nseg = (uint32_t)bk.nseg, units = nseg * (uint32_t)cx.N;
+  const uint32_t ph = slices_heavy(cx, units), pc = slices_cap(cx, units, 32);
+  const uint32_t sh = slices_heavy(cx, nseg), sc = slices_cap(cx, nseg, 32);
+#define PUSH(S, P) run_units(cx, units, P, [&](int y, uint32_t x, uint32_t nx) { push_stage<S>(bk, cm, cx, sm, y, x, nx); })
+#define SRV(S, P) run_units(cx, nseg, P, [&](int y, uint32_t x, uint32_t nx) { server_stage<S>(bk, cm, cx, sm, y, x, nx); })
+  PUSH(0, ph);
+  sp_barrier(cm, cx, sm);
+  PUSH(1, ph);
+  // the gradient has been read (it may be the result buffer): clear the result
+  run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
+  sp_barrier(cm, cx, sm);
+  const bool ovf = any_overflow(cx.ws, units, sm);
+  PUSH(2, pc);
+  sp_barrier(cm, cx, sm);
+  PUSH(3, pc);
+  sp_barrier(cm, cx, sm);
+  PUSH(4, pc);
+  if (ovf) {
+    PUSH(5, ph);
+    sp_barrier(cm, cx, sm);
+    PUSH(6, ph);
+    sp_barrier(cm, cx, sm);
+    PUSH(7, ph);
+  }
+  SRV(0, sh);
+  sp_barrier(cm, cx, sm);
+  SRV(1, sh);
+  sp_barrier(cm, cx, sm);
+  SRV(2, sh);
+  sp_barrier(cm, cx, sm);
+  const bool ovf2 = any_overflow(cx.ws + (size_t)units * kWsWords, nseg, sm);
+  SRV(3, sc);
+  sp_barrier(cm, cx, sm);
+  SRV(4, sc);
+  sp_barrier(cm, cx, sm);
+  SRV(5, sc);
+  if (ovf2) {
+    SRV(6, sh);
+    sp_barrier(cm, cx, sm);
+    SRV(7, sh);
+    sp_barrier(cm, cx, sm);
+    SRV(8, sh);
+  }
+  const int N = cx.N;
+  run_units(cx, units, slices_cap(cx, units, 16), [&](int y, uint32_t x, uint32_t nx) {
+    const int j = y % N;
+    gather_stage(bk, cm, cx, sm, y / N, N + j, j, 5u, x, nx);
+  });
+#undef PUSH
+#undef SRV
+}
+
+// Ring: N hops of (add the predecessor's pairs, update, select, store into the
+// successor's inbox), the last hop storing into every inbox; then every rank scatters
+// the N reduced chunks.  Five barriers per hop when no candidate list overflows.
+__global__ void __launch_bounds__(kSpThreads, 3)
+sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
+  __shared__ SpSmem sm;
+  SpCtx cx;
+  sp_prologue(cm, L, cx, sm);
+  const int N = cx.N;
+  const uint32_t nseg = (uint32_t)bk.nseg;
+  const uint32_t sh = slices_heavy(cx, nseg), sc = slices_cap(cx, nseg, 32);
+#define HOP(S, P) run_units(cx, nseg, P, [&](int y, uint32_t x, uint32_t nx) { ring_stage<S>(bk, cm, cx, sm, hop, y, x, nx); })
+  for (int hop = 0; hop < N; ++hop) {
+    if (hop > 0) {
+      HOP(0, sc);
+      sp_barrier(cm, cx, sm);
+    }
+    HOP(1, sh);
+    sp_barrier(cm, cx, sm);
+    HOP(2, sh);
+    if (hop == N - 1)  // every chunk of the gradient has been read: clear the result
+      run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
+    sp_barrier(cm, cx, sm);
+    const bool ovf = any_overflow(cx.ws + (size_t)hop * nseg * kWsWords, nseg, sm);
+    HOP(3, sc);
+    sp_barrier(cm, cx, sm);
+    HOP(4, sc);
+    sp_barrier(cm, cx, sm);
+    HOP(5, sc);
+    if (ovf) {
+      HOP(6, sh);
+      sp_barrier(cm, cx, sm);
+      HOP(7, sh);
+      sp_barrier(cm, cx, sm);
+      HOP(8, sh);
+    }
+  }
+#undef HOP
+  // gather: rank src finalised chunk src + 1
+  const uint32_t units = nseg * (uint32_t)N;
+  run_units(cx, units, slices_cap(cx, units, 16), [&](int y, uint32_t x, uint32_t nx) {
+    const int src = y % N;
+    gather_stage(bk, cm, cx, sm, y / N, N - 1 + src, (src + 1) % N, 7u, x, nx);
+  });
 }
 
 static int build_sp_bucket(int alg, float ratio, float momentum, const HpSeg* segs,
@@ -402,6 +563,53 @@ static int build_sp_bucket(int alg, float ratio, float momentum, const HpSeg* se
   return 0;
 }
 
+// ------------------------------------------------------------------ host side
+static uint64_t sp_hist_words(int nseg, int nranks) {
+  return (uint64_t)(nseg * nranks + nseg) * kWsWords;   // the ring uses nseg * nranks of them
+}
+
+static int launch_sparse(int topo, const SpBucket& bk, const HpComm& cm, void* ws, int ctas,
+                         cudaStream_t st) {
+  const void* kern = topo == HP_TOPO_RING ? (const void*)sp_ring_kernel : (const void*)sp_ps_kernel;
+  const int N = cm.nranks, nseg = bk.nseg;
+  static int resident[2][64] = {};   // CTAs the GPU holds at once, per (topology, device)
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  int cap = (dev >= 0 && dev < 64) ? resident[topo][dev] : 0;
+  if (cap == 0) {
+    int sms = 0, per_sm = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kSpThreads, 0);
+    if (e != cudaSuccess) return (int)e;
+    cap = per_sm * sms;
+    if (cap < 1) return HP_ERR_RESIDENCY;
+    if (dev >= 0 && dev < 64) resident[topo][dev] = cap;
+  }
+  const int ranks_here = cm.emulate ? N : 1;
+  int G = ctas;
+  if (G <= 0) {   // a quarter of the bucket's tiles, at least 32, at most what the GPU holds
+    uint64_t tiles = 0;
+    for (int i = 0; i < nseg; ++i) tiles += (bk.seg[i].n + kTile - 1) / kTile;
+    G = (int)(tiles / 4 < 32 ? 32 : (tiles / 4 > 592 ? 592 : tiles / 4));
+    if (G > cap / ranks_here) G = cap / ranks_here;
+  }
+  if (G < 1 || (long long)G * ranks_here > (long long)cap) return HP_ERR_RESIDENCY;
+  SpLaunch L;
+  L.ws = static_cast<uint8_t*>(ws);
+  L.hist_words = sp_hist_words(nseg, N);
+  L.hist_bytes = align_up((L.hist_words + kCtlWords) * 4, 256);
+  L.ws_rank_bytes = L.hist_bytes + bk.cand_pairs * 8;
+  for (int r = 0; r < ranks_here; ++r) {  // histograms, counters and control words start at zero
+    e = cudaMemsetAsync(L.ws + (size_t)r * L.ws_rank_bytes, 0, (L.hist_words + kCtlWords) * 4, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  void* args[] = {(void*)&bk, (void*)&cm, (void*)&L};
+  // cooperative: the CTAs of a launch wait for one another at the phase barriers
+  e = cudaLaunchCooperativeKernel(kern, dim3(G, ranks_here), dim3(kSpThreads), args, 0, st);
+  return (int)e;
+}
+
 }  // namespace hipress
 
 using namespace hipress;
@@ -419,134 +627,38 @@ int hp_fused_sparse_layout(float ratio, const uint64_t* ns, int nseg, int nranks
   if (rc) return rc;
   if (inbox_bytes) *inbox_bytes = bk.slot_bytes * 2ull * nranks;
   if (flag_words) *flag_words = 2ull * nranks * nseg;
-  // push units (nseg * nranks) + server units (nseg), per emulated rank
+  // per rank played by a launch: histogram blocks of the push (nseg * nranks) and
+  // server (nseg) units, control words, candidate lists
   if (ws_bytes)
-    *ws_bytes = align_up((uint64_t)(nseg * nranks + nseg) * kWsWords * 4, 256) + bk.cand_pairs * 8;
+    *ws_bytes = align_up((sp_hist_words(nseg, nranks) + kCtlWords) * 4, 256) + bk.cand_pairs * 8;
   return 0;
 }
 
-// One synchronisation of a bucket through the PS topology.  segs[i].r is the
-// accumulator (DGC v / GradDrop residual), us[i] the DGC momentum (or NULL),
-// segs[i].sr the server accumulator of the owned chunk.  ws: zero-initialised
-// scratch of hp_fused_sparse_layout().ws_bytes per rank played by this call.
+// One synchronisation of a bucket through the PS topology: one cooperative launch.
+// segs[i].r is the accumulator (DGC v / GradDrop residual), us[i] the DGC momentum
+// (or NULL), segs[i].sr the server accumulator of the owned chunk.  ws: scratch of
+// hp_fused_sparse_layout().ws_bytes per rank played by this call.  ctas <= 0: the
+// grid is sized from the bucket.
 int hp_cuda_fused_sparse_ps(int alg, float ratio, float momentum, const HpSeg* segs,
                             void* const* us, int nseg, const HpComm* comm, void* ws, int ctas,
                             void* stream) {
   if (!comm || ctas > 1024) return HP_ERR_BAD_ARG;
   SpBucket bk;
-  const int N = comm->nranks;
-  int rc = build_sp_bucket(alg, ratio, momentum, segs, nullptr, us, nseg, N, bk);
+  int rc = build_sp_bucket(alg, ratio, momentum, segs, nullptr, us, nseg, comm->nranks, bk);
   if (rc) return rc;
-  cudaStream_t st = (cudaStream_t)stream;
-  const int ranks_here = comm->emulate ? N : 1;
-  const size_t hist_words = (size_t)(nseg * N + nseg) * kWsWords;
-  const size_t hist_bytes = align_up(hist_words * 4, 256);
-  const size_t ws_rank_bytes = hist_bytes + bk.cand_pairs * 8;
-  uint8_t* wsb = static_cast<uint8_t*>(ws);
-  for (int r = 0; r < ranks_here; ++r) {  // only the histogram blocks need clearing
-    cudaError_t e = cudaMemsetAsync(wsb + (size_t)r * ws_rank_bytes, 0, hist_words * 4, st);
-    if (e != cudaSuccess) return (int)e;
-  }
-  // ctas <= 0: size the grids so that every launch fills the GPU about four
-  // CTAs per SM, whatever the number of (tensor, owner) units
-  auto per_unit = [&](int units) {
-    if (ctas > 0) return ctas;
-    int c = (148 * 4 + units - 1) / units;
-    return c < 4 ? 4 : (c > 592 ? 592 : c);
-  };
-  const dim3 gpush(per_unit(nseg * N), nseg * N), gsrv(per_unit(nseg), nseg);
-  const dim3 cpush(gpush.x < 32 ? gpush.x : 32, nseg * N), csrv(gsrv.x < 32 ? gsrv.x : 32, nseg);
-  const dim3 gpull(per_unit(nseg * N) < 16 ? per_unit(nseg * N) : 16, nseg * N);
-  // With emulated ranks every phase is issued for all ranks before the next one,
-  // so a wait never targets a launch that is still queued behind it.
-  for (int r = 0; r < ranks_here; ++r) {
-    const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
-    uint32_t* w = reinterpret_cast<uint32_t*>(wsb + (size_t)r * ws_rank_bytes);
-    uint8_t* cd = wsb + (size_t)r * ws_rank_bytes + hist_bytes;
-    sp_push_kernel<0><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_push_kernel<1><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_push_kernel<2><<<cpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_push_kernel<3><<<cpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_push_kernel<4><<<cpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_push_kernel<5><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_push_kernel<6><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_push_kernel<7><<<gpush, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-  }
-  for (int r = 0; r < ranks_here; ++r) {
-    const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
-    uint32_t* w = reinterpret_cast<uint32_t*>(wsb + (size_t)r * ws_rank_bytes) +
-                  (size_t)nseg * N * kWsWords;
-    uint8_t* cd = wsb + (size_t)r * ws_rank_bytes + hist_bytes;
-    sp_server_kernel<0><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<1><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<2><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<3><<<csrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<4><<<csrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<5><<<csrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<6><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<7><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-    sp_server_kernel<8><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E, w, cd);
-  }
-  for (int r = 0; r < ranks_here; ++r) {
-    const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
-    sp_pull_kernel<0><<<gsrv, kSpThreads, 0, st>>>(bk, *comm, R, E);
-    sp_pull_kernel<1><<<gpull, kSpThreads, 0, st>>>(bk, *comm, R, E);
-  }
-  return (int)cudaGetLastError();
+  return launch_sparse(HP_TOPO_PS, bk, *comm, ws, ctas, (cudaStream_t)stream);
 }
 
-// One synchronisation of a bucket through the ring topology: N hops, each a fixed
-// sequence of launches over all tensors of the bucket, then the gather.  Same
-// arguments as hp_cuda_fused_sparse_ps (segs[i].sr is not used).
+// One synchronisation of a bucket through the ring topology: one cooperative launch.
+// Same arguments as hp_cuda_fused_sparse_ps (segs[i].sr is not used).
 int hp_cuda_fused_sparse_ring(int alg, float ratio, float momentum, const HpSeg* segs,
                               void* const* us, int nseg, const HpComm* comm, void* ws, int ctas,
                               void* stream) {
   if (!comm || ctas > 1024) return HP_ERR_BAD_ARG;
   SpBucket bk;
-  const int N = comm->nranks;
-  int rc = build_sp_bucket(alg, ratio, momentum, segs, nullptr, us, nseg, N, bk);
+  int rc = build_sp_bucket(alg, ratio, momentum, segs, nullptr, us, nseg, comm->nranks, bk);
   if (rc) return rc;
-  cudaStream_t st = (cudaStream_t)stream;
-  const int ranks_here = comm->emulate ? N : 1;
-  const size_t hist_words = (size_t)(nseg * N + nseg) * kWsWords;  // ring uses nseg * N of them
-  const size_t hist_bytes = align_up(hist_words * 4, 256);
-  const size_t ws_rank_bytes = hist_bytes + bk.cand_pairs * 8;
-  uint8_t* wsb = static_cast<uint8_t*>(ws);
-  for (int r = 0; r < ranks_here; ++r) {
-    cudaError_t e = cudaMemsetAsync(wsb + (size_t)r * ws_rank_bytes, 0, hist_words * 4, st);
-    if (e != cudaSuccess) return (int)e;
-  }
-  auto per_unit = [&](int units) {
-    if (ctas > 0) return ctas;
-    int c = (148 * 4 + units - 1) / units;
-    return c < 4 ? 4 : (c > 592 ? 592 : c);
-  };
-  const dim3 gh(per_unit(nseg), nseg), ch(gh.x < 32 ? gh.x : 32, nseg);
-  const dim3 gpull(per_unit(nseg * N) < 16 ? per_unit(nseg * N) : 16, nseg * N);
-  // hop-major order: with emulated ranks the producer of a hop's input has
-  // always been issued before its consumer
-  for (int hop = 0; hop < N; ++hop) {
-    for (int r = 0; r < ranks_here; ++r) {
-      const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
-      uint32_t* w = reinterpret_cast<uint32_t*>(wsb + (size_t)r * ws_rank_bytes);
-      uint8_t* cd = wsb + (size_t)r * ws_rank_bytes + hist_bytes;
-      if (hop > 0) sp_ring_kernel<0><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<1><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<2><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<3><<<ch, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<4><<<ch, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<5><<<ch, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<6><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<7><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-      sp_ring_kernel<8><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E, hop, w, cd);
-    }
-  }
-  for (int r = 0; r < ranks_here; ++r) {
-    const int R = comm->emulate ? r : comm->rank, E = comm->emulate ? r : 0;
-    sp_pull_kernel<0><<<gh, kSpThreads, 0, st>>>(bk, *comm, R, E);
-    sp_ring_gather_kernel<<<gpull, kSpThreads, 0, st>>>(bk, *comm, R, E);
-  }
-  return (int)cudaGetLastError();
+  return launch_sparse(HP_TOPO_RING, bk, *comm, ws, ctas, (cudaStream_t)stream);
 }
 
 }  // extern "C"

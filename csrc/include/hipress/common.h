@@ -126,12 +126,10 @@ HP_HD float u01(uint32_t r) { return (float)(r >> 8) * (1.0f / 16777216.0f); }
 // call is keyed by q with bit 8 cleared; float4 q takes the low halves of the four
 // words when its bit 8 is clear and the high halves when it is set.  A pure function
 // of the element index, so the CPU oracle and every kernel layout draw the same
-// numbers.  Sixteen bits bound the rounding bias by 2^-17 of a quantisation step.
+// numbers.
 HP_HD uint32_t rnd16_counter(uint64_t elem) { return (uint32_t)(elem >> 2) & ~256u; }
 HP_HD uint32_t rnd16_half(uint64_t elem) { return (uint32_t)(elem >> 10) & 1u; }
-HP_HD float u01_16(uint32_t word, uint32_t half) {
-  return (float)((word >> (16u * half)) & 0xFFFFu) * (1.0f / 65536.0f);
-}
+HP_HD uint32_t rnd16(uint32_t word, uint32_t half) { return half ? (word >> 16) : (word & 0xFFFFu); }
 
 // ---------------------------------------------------------------------------
 // Parameters shared by every dense (quantising) algorithm
@@ -165,16 +163,31 @@ HP_HD float onebit_value(uint32_t code, float s) { return code ? -s : s; }
 HP_HD float tern_gap(float mn, float mx, int bits) {
   return (mx - mn) / (float)((1u << bits) - 1u);
 }
-// inv_gap = 1 / gap, computed once per tile (a multiply per element instead of a
-// division; both implementations round the same way)
-HP_HD float tern_inv_gap(float gap) { return gap > 0.0f ? 1.0f / gap : 0.0f; }
-HP_HD uint32_t tern_code(float x, float mn, float inv_gap, float u, int bits) {
-  if (!(inv_gap > 0.0f)) return 0u;
-  float q = floorf((x - mn) * inv_gap + u);
-  float qmax = (float)((1u << bits) - 1u);
-  if (!(q > 0.0f)) q = 0.0f;   // also catches NaN
-  if (q > qmax) q = qmax;
-  return (uint32_t)q;
+// Stochastic rounding in fixed point.  scale16 = 65536 / gap is computed once per
+// tile; per element t = floor((x - min) * scale16) is the position in units of
+// 2^-16 of a quantisation step, and q = (t + u16) >> 16 with a 16-bit uniform u16
+// rounds up with probability frac(t / 65536): unbiased to 2^-16 of a step.  Integer
+// adds and shifts replace a floor, two compares and a float conversion per element;
+// t < 2^24 for every supported bit width, so the float product is exact enough to
+// keep level placement within one step.  The conversion saturates and maps NaN to 0
+// on both implementations.
+HP_HD float tern_scale16(float gap) { return gap > 0.0f ? 65536.0f / gap : 0.0f; }
+HP_HD int32_t f2i_floor_sat(float t) {
+#if defined(__CUDA_ARCH__)
+  return __float2int_rd(t);
+#else
+  if (!(t == t)) return 0;
+  if (t >= 2147483648.0f) return 2147483647;
+  if (t <= -2147483648.0f) return (int32_t)(-2147483647 - 1);
+  return (int32_t)floorf(t);
+#endif
+}
+HP_HD uint32_t tern_code(float x, float mn, float scale16, uint32_t u16, int bits) {
+  if (!(scale16 > 0.0f)) return 0u;
+  const uint32_t t = (uint32_t)f2i_floor_sat((x - mn) * scale16);
+  const uint32_t q = (t + u16) >> 16;
+  const uint32_t qmax = (1u << bits) - 1u;
+  return q > qmax ? qmax : q;
 }
 HP_HD float tern_value(uint32_t q, float mn, float gap) {
   return fmaf((float)q, gap, mn);

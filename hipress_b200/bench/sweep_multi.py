@@ -82,6 +82,8 @@ def main(argv=None):
         s *= 4
     rows = []
     status = torch.zeros(4, dtype=torch.int32, device=dev)
+    tick = torch.zeros(1, device=dev)
+    align = (lambda: dist.all_reduce(tick)) if N > 1 else None
     for nbytes in sizes:
         n = nbytes // 4
         gen = torch.Generator(dev).manual_seed(R)
@@ -89,7 +91,7 @@ def main(argv=None):
         work = torch.empty_like(g)
         if N > 1:
             t = time_cuda(lambda: dist.all_reduce(work), iters=a.iters, flush=flush,
-                          setup=lambda: work.copy_(g))
+                          setup=lambda: work.copy_(g), align=align)
             ar_ms = _max_over_ranks(t["median_ms"])
         else:
             ar_ms = 0.0
@@ -124,7 +126,7 @@ def main(argv=None):
                             [work.data_ptr()], [None if r is None else r.data_ptr()], [work.data_ptr()],
                             [sr.data_ptr() if r is not None else None])
                     dist.barrier() if N > 1 else None
-                    t = time_cuda(fn, iters=a.iters, flush=flush, setup=lambda: work.copy_(g))
+                    t = time_cuda(fn, iters=a.iters, flush=flush, setup=lambda: work.copy_(g), align=align)
                     row["fused_ms"] = round(_max_over_ranks(t["median_ms"]) if N > 1 else t["median_ms"], 5)
                     roof = roofline_ms(comp, n, N, topo, peaks)
                     row.update({k: round(v, 5) for k, v in roof.items()})
@@ -149,7 +151,7 @@ def main(argv=None):
                     sst = {"residual": sr} if (comp.spec.sparse or "residual" in st2) else {}
                     seg = [SegView(work, st2, sst, 0)]
                     t = time_cuda(lambda: hs.sync(seg), iters=max(2, a.iters // 2), warmup=1, flush=flush,
-                                  setup=lambda: work.copy_(g))
+                                  setup=lambda: work.copy_(g), align=align)
                     row["unfused_ms"] = round(_max_over_ranks(t["median_ms"]) if N > 1 else t["median_ms"], 5)
                 if "fused_ms" in row:
                     if N > 1:

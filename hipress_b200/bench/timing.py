@@ -38,8 +38,19 @@ class L2Flusher:
         self.sink = self.rd.sum()
 
 
-def time_cuda(fn, *, warmup=3, iters=10, flush: L2Flusher | None = None, setup=None):
-    """Median / min milliseconds of fn() over `iters` runs timed with CUDA events."""
+def time_cuda(fn, *, warmup=3, iters=10, flush: L2Flusher | None = None, setup=None,
+              hide_launch: bool = True, align=None):
+    """Median / min milliseconds of fn() over `iters` runs timed with CUDA events.
+
+    ``hide_launch`` (default): the first event and fn()'s launches are queued while
+    earlier work (the L2 flush, or a short spin kernel) still occupies the stream, so
+    the interval between the events is device time only -- what a training step
+    sees, where a bucket's launch is queued behind backward kernels.  With
+    ``hide_launch=False`` the stream is idle when fn() is called and the host's
+    launch path (tens of microseconds from Python) is part of the figure.
+    ``align`` (multi-GPU runs): a callable that queues a tiny collective right before
+    the first event, so every rank's timed region starts at the same moment on the
+    device instead of whenever its host got there."""
     for _ in range(warmup):
         if setup:
             setup()
@@ -49,10 +60,16 @@ def time_cuda(fn, *, warmup=3, iters=10, flush: L2Flusher | None = None, setup=N
     for _ in range(iters):
         if setup:
             setup()
+        torch.cuda.synchronize()
         if flush:
             flush()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
+        if not hide_launch:
+            torch.cuda.synchronize()
+        else:
+            torch.cuda._sleep(400_000)      # ~0.2 ms of spinning: time to queue what follows
+        if align is not None:
+            align()
         a.record()
         fn()
         b.record()

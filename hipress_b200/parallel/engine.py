@@ -480,7 +480,7 @@ class GradSyncEngine:
                 sr_ptrs.append(sst["residual"].data_ptr() if "residual" in sst else None)
             b.impl.launch_ptrs(g_ptrs, a_ptrs, u_ptrs, g_ptrs, sr_ptrs,
                                stream=b.stream or self.comm_stream)
-            self.launch_count += 19 if self.cfg.topology == "ps" else 9 * self.N + 1
+            self.launch_count += 1
         elif b.impl is not None:
             g_ptrs, r_ptrs, sr_ptrs, ids = [], [], [], []
             rname = "residual"

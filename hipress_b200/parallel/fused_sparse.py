@@ -1,7 +1,7 @@
-"""Python face of the fused sparse parameter-server kernels
-(csrc/cuda/fused_sparse.cu): DGC / GradDrop buckets synchronised by a fixed
-sequence of launches that select, store (index, value) pairs into peer GPUs'
-inboxes, re-select at the owner and scatter the result -- no NCCL call."""
+"""Python face of the fused sparse kernels (csrc/cuda/fused_sparse.cu): a DGC /
+GradDrop bucket is synchronised by ONE persistent cooperative launch that selects,
+stores (index, value) pairs into peer GPUs' inboxes, re-selects (at the owner for
+PS, at every hop for the ring) and scatters the result -- no NCCL call."""
 from __future__ import annotations
 
 import ctypes as C
@@ -93,7 +93,7 @@ class FusedSparseBucket:
                 self.sizes[i], i
             self._us[i] = u_ptrs[i] if u_ptrs is not None else None
         cm = self._comm
-        self.epoch += 1
+        self.epoch = self.epoch % 0x7FFFFFFE + 1     # 31 bits: the top bit of a flag is a mark
         cm.nranks, cm.rank, cm.emulate = self.nranks, self.rank, 1 if self.emulate else 0
         cm.epoch, cm.timeout_ns = self.epoch, self.timeout_ns
         for q in range(self.nranks):

@@ -172,3 +172,62 @@ def test_overlapped_optimizer_step_on_the_communication_stream():
     assert len(plain) == len(over) == 12
     for a, b in zip(plain, over):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("topology", ["ps", "ring"])
+def test_sparse_auto_grid_and_heavy_ties(topology):
+    """Grid sized from the bucket (ctas=0) and a gradient made of few distinct
+    magnitudes, so the candidate list of the threshold bin overflows and the
+    full-array passes (the extra, conditional phases of the launch) decide."""
+    torch.manual_seed(21)
+    N, n = 2, 600000
+    c = Compressor("graddrop", ratio=0.01)
+    b = FusedSparseBucket(c.spec, [n], N, 0, ctas=0, emulate=True, topology=topology).bind_local("cuda")
+    G = (torch.randint(0, 3, (N, n)).float() - 1.0).cuda()        # values -1, 0, +1: massive ties
+    A = torch.zeros(N, n, device="cuda")
+    O = torch.zeros(N, n, device="cuda")
+    SR = torch.zeros(N, chunk_elems(n, N), device="cuda")
+    b.launch_ptrs([G.data_ptr()], [A.data_ptr()], None, [O.data_ptr()],
+                  [SR.data_ptr() if topology == "ps" else None], strides=(n, n, n, SR.shape[1]))
+    torch.cuda.synchronize()
+    b.check_status()
+    assert torch.equal(O[0], O[1])
+    k = c.kmax(chunk_elems(n, N))
+    sent = int((O[0] != 0).sum())
+    assert 0 < sent <= 2 * k
+    # conservation: what was delivered plus what every rank (and owner) kept is the input
+    kept = A.sum(0)
+    if topology == "ps":
+        kept[:SR.shape[1]] += SR[0][:min(n, SR.shape[1])]
+        kept[SR.shape[1]:] += SR[1][:n - SR.shape[1]]
+    assert torch.allclose(O[0] * N + kept, G.sum(0), atol=1e-5)
+
+
+def test_sparse_kernel_gives_up_cleanly_when_a_peer_never_sends():
+    """Rank 0 of a two-rank job whose peer does not exist: the flag it waits for is
+    never set.  The waits and the phase barriers are bounded, the launch ends by
+    itself and the status word names the wait."""
+    import time
+    from hipress_b200.parallel.fused import HipressTimeoutError
+    c = Compressor("graddrop", ratio=0.01)
+    n = 50000
+    b = FusedSparseBucket(c.spec, [n], 2, 0, ctas=8, timeout_s=0.3, topology="ps")
+    arena = torch.zeros(2 * b.region_bytes(), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    b.bind([arena.data_ptr(), arena.data_ptr() + b.region_bytes()], status, "cuda")
+    g = torch.randn(n, device="cuda")
+    a = torch.zeros(n, device="cuda")
+    out = torch.full((n,), 5.0, device="cuda")
+    sr = torch.zeros(chunk_elems(n, 2), device="cuda")
+    t0 = time.time()
+    b.launch_ptrs([g.data_ptr()], [a.data_ptr()], None, [out.data_ptr()], [sr.data_ptr()])
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 10.0
+    with pytest.raises(HipressTimeoutError):
+        b.check_status()
+    # still usable afterwards
+    b1 = FusedSparseBucket(c.spec, [n], 1, 0, ctas=8).bind_local("cuda")
+    b1.launch_ptrs([g.data_ptr()], [torch.zeros_like(g).data_ptr()], None, [out.data_ptr()],
+                   [torch.zeros(chunk_elems(n, 1), device="cuda").data_ptr()])
+    torch.cuda.synchronize()
+    b1.check_status()
