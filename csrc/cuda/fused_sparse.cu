@@ -78,7 +78,8 @@ struct SpSmem {
 // control words of one rank played by a launch, behind its histogram blocks; zero
 // when the kernel starts (cleared with the histograms)
 constexpr int kCtlBarrier = 0;
-constexpr int kCtlWords = 16;
+constexpr int kCtlStamps = 8;    // low 32 bits of %globaltimer: kernel start, then after every barrier
+constexpr int kCtlWords = 128;
 
 struct SpCtx {
   int N, R, E;
@@ -99,6 +100,14 @@ __device__ __forceinline__ void sp_barrier(const HpComm& cm, SpCtx& cx, SpSmem& 
   // a peer may be late by up to one wait bound before a CTA reaches the barrier
   grid_barrier(cx.ctl + kCtlBarrier, cx.gen, cx.G, 2 * cm.timeout_ns + 1000000000ull, cx.status,
                HP_STATUS_TIMEOUT | (8u << 16) | (cx.gen & 255u), sm.wst);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && kCtlStamps + cx.gen < (uint32_t)kCtlWords)
+    cx.ctl[kCtlStamps + cx.gen] = (uint32_t)global_timer_ns();
+}
+
+// between two stages that one CTA runs back to back on the same unit
+__device__ __forceinline__ void cta_fence_sync() {
+  __threadfence();
+  __syncthreads();
 }
 
 // Phase driver: `units` work units, each cut into `per` slices; slice v of the phase
@@ -416,12 +425,23 @@ __device__ __forceinline__ void sp_prologue(const HpComm& cm, const SpLaunch& L,
   cx.cand = base + L.hist_bytes;
   cx.status = reinterpret_cast<uint32_t*>(cm.status) + 4 * cx.E;
   cx.gen = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) cx.ctl[kCtlStamps] = (uint32_t)global_timer_ns();
   wait_init(sm.wst);
+}
+
+// CTA 0's last stamp and the number of barriers it passed (the other CTAs may still
+// be scattering: the stamps are a profile of the phases, not a completion signal)
+__device__ __forceinline__ void sp_epilogue(const SpCtx& cx) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (kCtlStamps + cx.gen + 1 < (uint32_t)kCtlWords)
+      cx.ctl[kCtlStamps + cx.gen + 1] = (uint32_t)global_timer_ns();
+    cx.ctl[1] = cx.gen;
+  }
 }
 
 // PS: push (every rank selects per owner and stores the pairs into the owner's
 // inbox), server (the owner adds the N payloads, re-selects, stores the result into
-// every inbox), pull (every rank scatters value / N).  11 barriers when no candidate
+// every inbox), pull (every rank scatters value / N).  Five barriers when no candidate
 // list overflows.
 __global__ void __launch_bounds__(kSpThreads, 3)
 sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
@@ -429,8 +449,7 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   SpCtx cx;
   sp_prologue(cm, L, cx, sm);
   const uint32_t nseg = (uint32_t)bk.nseg, units = nseg * (uint32_t)cx.N;
-  const uint32_t ph = slices_heavy(cx, units), pc = slices_cap(cx, units, 32);
-  const uint32_t sh = slices_heavy(cx, nseg), sc = slices_cap(cx, nseg, 32);
+  const uint32_t ph = slices_heavy(cx, units), sh = slices_heavy(cx, nseg);
 #define PUSH(S, P) run_units(cx, units, P, [&](int y, uint32_t x, uint32_t nx) { push_stage<S>(bk, cm, cx, sm, y, x, nx); })
 #define SRV(S, P) run_units(cx, nseg, P, [&](int y, uint32_t x, uint32_t nx) { server_stage<S>(bk, cm, cx, sm, y, x, nx); })
   PUSH(0, ph);
@@ -440,11 +459,15 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
   sp_barrier(cm, cx, sm);
   const bool ovf = any_overflow(cx.ws, units, sm);
-  PUSH(2, pc);
-  sp_barrier(cm, cx, sm);
-  PUSH(3, pc);
-  sp_barrier(cm, cx, sm);
-  PUSH(4, pc);
+  // the candidate list of a unit is short (about as many pairs as are sent): one CTA
+  // takes a unit through both digit passes and the compaction, no barrier in between
+  run_units(cx, units, 1, [&](int y, uint32_t x, uint32_t nx) {
+    push_stage<2>(bk, cm, cx, sm, y, x, nx);
+    cta_fence_sync();
+    push_stage<3>(bk, cm, cx, sm, y, x, nx);
+    cta_fence_sync();
+    push_stage<4>(bk, cm, cx, sm, y, x, nx);
+  });
   if (ovf) {
     PUSH(5, ph);
     sp_barrier(cm, cx, sm);
@@ -459,11 +482,13 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   SRV(2, sh);
   sp_barrier(cm, cx, sm);
   const bool ovf2 = any_overflow(cx.ws + (size_t)units * kWsWords, nseg, sm);
-  SRV(3, sc);
-  sp_barrier(cm, cx, sm);
-  SRV(4, sc);
-  sp_barrier(cm, cx, sm);
-  SRV(5, sc);
+  run_units(cx, nseg, 1, [&](int y, uint32_t x, uint32_t nx) {
+    server_stage<3>(bk, cm, cx, sm, y, x, nx);
+    cta_fence_sync();
+    server_stage<4>(bk, cm, cx, sm, y, x, nx);
+    cta_fence_sync();
+    server_stage<5>(bk, cm, cx, sm, y, x, nx);
+  });
   if (ovf2) {
     SRV(6, sh);
     sp_barrier(cm, cx, sm);
@@ -478,11 +503,12 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   });
 #undef PUSH
 #undef SRV
+  sp_epilogue(cx);
 }
 
 // Ring: N hops of (add the predecessor's pairs, update, select, store into the
 // successor's inbox), the last hop storing into every inbox; then every rank scatters
-// the N reduced chunks.  Five barriers per hop when no candidate list overflows.
+// the N reduced chunks.  Three barriers per hop when no candidate list overflows.
 __global__ void __launch_bounds__(kSpThreads, 3)
 sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   __shared__ SpSmem sm;
@@ -504,11 +530,13 @@ sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
       run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
     sp_barrier(cm, cx, sm);
     const bool ovf = any_overflow(cx.ws + (size_t)hop * nseg * kWsWords, nseg, sm);
-    HOP(3, sc);
-    sp_barrier(cm, cx, sm);
-    HOP(4, sc);
-    sp_barrier(cm, cx, sm);
-    HOP(5, sc);
+    run_units(cx, nseg, 1, [&](int y, uint32_t x, uint32_t nx) {
+      ring_stage<3>(bk, cm, cx, sm, hop, y, x, nx);
+      cta_fence_sync();
+      ring_stage<4>(bk, cm, cx, sm, hop, y, x, nx);
+      cta_fence_sync();
+      ring_stage<5>(bk, cm, cx, sm, hop, y, x, nx);
+    });
     if (ovf) {
       HOP(6, sh);
       sp_barrier(cm, cx, sm);
@@ -524,6 +552,7 @@ sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
     const int src = y % N;
     gather_stage(bk, cm, cx, sm, y / N, N - 1 + src, (src + 1) % N, 7u, x, nx);
   });
+  sp_epilogue(cx);
 }
 
 static int build_sp_bucket(int alg, float ratio, float momentum, const HpSeg* segs,

@@ -40,7 +40,7 @@ __device__ __forceinline__ void find_bin(const uint32_t* __restrict__ hist, uint
   uint32_t sum = 0;
 #pragma unroll
   for (int i = 0; i < per; ++i) {
-    c[i] = hist[threadIdx.x * per + i];
+    c[i] = __ldcg(hist + threadIdx.x * per + i);  // written by other CTAs' atomics: read at L2
     sum += c[i];
   }
   fs.sums[threadIdx.x] = sum;

@@ -115,7 +115,8 @@ def run_single(alg, topo, mbytes, ctas, iters, out):
         gbs = nbytes / (t["median_ms"] * 1e-3) / 1e9
         row = {"kernel": f"{topo}_{alg}_1rank", "mbytes": mbytes, "ms": round(t["median_ms"], 5),
                "gbs": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
-               "peak_source": peaks["source"]}
+               "peak_source": peaks["source"],
+               "phase_end_ms": [round(x, 4) for x in b.last_phase_times()]}
         out.append(row)
         print(json.dumps(row), flush=True)
         return

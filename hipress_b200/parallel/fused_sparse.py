@@ -109,6 +109,18 @@ class FusedSparseBucket:
                 self.ctas, _lib.stream_ptr(stream))
         _lib.check(rc, "fused sparse launch")
 
+    def last_phase_times(self):
+        """Device-side profile of the last launch (rank 0 of an emulated launch): the
+        time in ms, from the kernel's start, at which CTA 0 left each phase barrier,
+        and last its own end.  %globaltimer stamps written by the kernel."""
+        WS_WORDS, STAMPS = 3 * 4096 + 16, 8      # kWsWords, kCtlStamps of the kernels
+        nseg = len(self.sizes)
+        ctl = (nseg * self.nranks + nseg) * WS_WORDS
+        w = self.ws[ctl:ctl + 128].cpu().tolist()
+        gen = w[1]
+        st = [(x & 0xFFFFFFFF) for x in w[STAMPS:STAMPS + min(gen + 2, 128 - STAMPS)]]
+        return [((x - st[0]) & 0xFFFFFFFF) * 1e-6 for x in st[1:]]
+
     def check_status(self):
         from .fused import HipressTimeoutError, decode_status
         words = self.status.cpu().tolist()

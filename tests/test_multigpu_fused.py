@@ -70,3 +70,66 @@ def test_fused_multigpu_matches_simulation(alg, topo):
                 assert torch.allclose(got, ref[r], rtol=1e-5, atol=1e-8), (alg, topo, step, i, r)
                 assert torch.equal(got, res[0]["outs"][step][i])
     assert res[0]["launches"] >= steps
+
+
+def _ddp_vs_optimizer(rank, world, alg, topo):
+    """The same one-tensor model trained through (a) DistributedDataParallel with the
+    compression hook and (b) DistributedOptimizer: both run the fused kernels on the
+    same layout (one tensor = one DDP bucket = one segment), so the parameters must
+    agree bit for bit; the function API takes the fused path as well."""
+    import hipress_b200 as hp
+    from torch.nn.parallel import DistributedDataParallel as DDP
+    from hipress_b200.parallel.hooks import FlatSyncer, ddp_comm_hook
+    dev = hp.device()
+    cfg = dict(algorithm=alg, topology=topo, comp_threshold=4096, threshold=1e-3, ratio=0.01, ctas=32,
+               timeout_s=5.0)
+
+    def data(step):
+        g = torch.Generator().manual_seed(1000 * step + rank)
+        return torch.randn(16, 512, generator=g).to(dev)
+
+    def model():
+        torch.manual_seed(0)
+        return torch.nn.Linear(512, 1024, bias=False).to(dev)
+
+    m1 = model()
+    ddp = DDP(m1, device_ids=[dev.index])
+    syncer = FlatSyncer(hp.HipressConfig(**cfg))
+    ddp.register_comm_hook(syncer, ddp_comm_hook)
+    o1 = torch.optim.SGD(m1.parameters(), lr=0.1)
+    m2 = model()
+    o2 = hp.DistributedOptimizer(torch.optim.SGD(m2.parameters(), lr=0.1), list(m2.named_parameters()), **cfg)
+    assert o2.engine.backend == "fused"
+    for step in range(3):
+        x = data(step)
+        o1.zero_grad()
+        ddp(x).square().mean().backward()
+        o1.step()
+        o2.zero_grad()
+        m2(x).square().mean().backward()
+        o2.step()
+    torch.cuda.synchronize()
+    syncer.check()
+    o2.engine.check()
+    t = torch.full((20000,), 0.02 * (rank + 1), device=dev)
+    fa = hp.allreduce(t, name="fa", algorithm="tbq", threshold=0.01)
+    res = {"ddp": m1.weight.detach().cpu(), "opt": m2.weight.detach().cpu(), "launches": syncer.launch_count,
+           "fa": fa.cpu()}
+    syncer.close()
+    o2.close()
+    from hipress_b200.parallel import comm
+    for s in comm._syncers.values():
+        s.close()
+    comm._syncers.clear()
+    return res
+
+
+@pytest.mark.parametrize("alg,topo", [("tbq", "ring"), ("onebit", "ps"), ("dgc", "ps")])
+def test_ddp_hook_runs_the_fused_kernels_and_matches_the_optimizer(alg, topo):
+    world = min(_world(), 4)
+    res = spawn(_ddp_vs_optimizer, world, alg, topo, backend="nccl")
+    for r in res:
+        assert r["launches"] == 3, "one fused launch per DDP bucket and step"
+        assert torch.equal(r["ddp"], r["opt"]), (alg, topo)
+        assert torch.equal(r["ddp"], res[0]["ddp"])
+        assert torch.equal(r["fa"], res[0]["fa"]) and float(r["fa"].abs().max()) > 0
