@@ -104,6 +104,12 @@ __device__ __forceinline__ void sp_barrier(const HpComm& cm, SpCtx& cx, SpSmem& 
     cx.ctl[kCtlStamps + cx.gen] = (uint32_t)global_timer_ns();
 }
 
+// extra stamps of CTA 0 inside a phase (profile words 64..)
+__device__ __forceinline__ void sp_mark(const SpCtx& cx, int id) {
+  if (blockIdx.x == 0 && threadIdx.x == 0 && 64 + id < kCtlWords)
+    cx.ctl[64 + id] = (uint32_t)global_timer_ns();
+}
+
 // between two stages that one CTA runs back to back on the same unit
 __device__ __forceinline__ void cta_fence_sync() {
   __threadfence();
@@ -134,6 +140,23 @@ __device__ __forceinline__ bool any_overflow(const uint32_t* ws, uint32_t units,
   __syncthreads();
   return r;
 }
+
+// longest candidate list among `units` units; same conditions as any_overflow
+__device__ __forceinline__ uint32_t max_candidates(const uint32_t* ws, uint32_t units, SpSmem& sm) {
+  if (threadIdx.x == 0) sm.any = 0;
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < units; i += kSpThreads)
+    atomicMax(&sm.any, __ldcg(ws + (size_t)i * kWsWords + kWsCandCount));
+  __syncthreads();
+  const uint32_t r = sm.any;
+  __syncthreads();
+  return r;
+}
+// A unit whose candidate list has at most this many pairs goes through both digit
+// passes and the compaction on ONE CTA with no barrier in between; longer lists
+// (a steady-state accumulator is dense just below its threshold) are shared out
+// over several CTAs again, with a barrier after each pass.
+constexpr uint32_t kSmallCand = 8192;
 
 __device__ __forceinline__ uint32_t slices_heavy(const SpCtx& cx, uint32_t units) {
   const uint32_t p = cx.G / (units ? units : 1);
@@ -441,15 +464,16 @@ __device__ __forceinline__ void sp_epilogue(const SpCtx& cx) {
 
 // PS: push (every rank selects per owner and stores the pairs into the owner's
 // inbox), server (the owner adds the N payloads, re-selects, stores the result into
-// every inbox), pull (every rank scatters value / N).  Five barriers when no candidate
-// list overflows.
+// every inbox), pull (every rank scatters value / N).  Five barriers when the
+// candidate lists are short, nine otherwise (more only after an overflow).
 __global__ void __launch_bounds__(kSpThreads, 3)
 sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   __shared__ SpSmem sm;
   SpCtx cx;
   sp_prologue(cm, L, cx, sm);
   const uint32_t nseg = (uint32_t)bk.nseg, units = nseg * (uint32_t)cx.N;
-  const uint32_t ph = slices_heavy(cx, units), sh = slices_heavy(cx, nseg);
+  const uint32_t ph = slices_heavy(cx, units), pc = slices_cap(cx, units, 32);
+  const uint32_t sh = slices_heavy(cx, nseg), sc = slices_cap(cx, nseg, 32);
 #define PUSH(S, P) run_units(cx, units, P, [&](int y, uint32_t x, uint32_t nx) { push_stage<S>(bk, cm, cx, sm, y, x, nx); })
 #define SRV(S, P) run_units(cx, nseg, P, [&](int y, uint32_t x, uint32_t nx) { server_stage<S>(bk, cm, cx, sm, y, x, nx); })
   PUSH(0, ph);
@@ -461,13 +485,21 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   const bool ovf = any_overflow(cx.ws, units, sm);
   // the candidate list of a unit is short (about as many pairs as are sent): one CTA
   // takes a unit through both digit passes and the compaction, no barrier in between
-  run_units(cx, units, 1, [&](int y, uint32_t x, uint32_t nx) {
-    push_stage<2>(bk, cm, cx, sm, y, x, nx);
-    cta_fence_sync();
-    push_stage<3>(bk, cm, cx, sm, y, x, nx);
-    cta_fence_sync();
-    push_stage<4>(bk, cm, cx, sm, y, x, nx);
-  });
+  if (max_candidates(cx.ws, units, sm) <= kSmallCand) {
+    run_units(cx, units, 1, [&](int y, uint32_t x, uint32_t nx) {
+      push_stage<2>(bk, cm, cx, sm, y, x, nx);
+      cta_fence_sync();
+      push_stage<3>(bk, cm, cx, sm, y, x, nx);
+      cta_fence_sync();
+      push_stage<4>(bk, cm, cx, sm, y, x, nx);
+    });
+  } else {
+    PUSH(2, pc);
+    sp_barrier(cm, cx, sm);
+    PUSH(3, pc);
+    sp_barrier(cm, cx, sm);
+    PUSH(4, pc);
+  }
   if (ovf) {
     PUSH(5, ph);
     sp_barrier(cm, cx, sm);
@@ -482,13 +514,21 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   SRV(2, sh);
   sp_barrier(cm, cx, sm);
   const bool ovf2 = any_overflow(cx.ws + (size_t)units * kWsWords, nseg, sm);
-  run_units(cx, nseg, 1, [&](int y, uint32_t x, uint32_t nx) {
-    server_stage<3>(bk, cm, cx, sm, y, x, nx);
-    cta_fence_sync();
-    server_stage<4>(bk, cm, cx, sm, y, x, nx);
-    cta_fence_sync();
-    server_stage<5>(bk, cm, cx, sm, y, x, nx);
-  });
+  if (max_candidates(cx.ws + (size_t)units * kWsWords, nseg, sm) <= kSmallCand) {
+    run_units(cx, nseg, 1, [&](int y, uint32_t x, uint32_t nx) {
+      server_stage<3>(bk, cm, cx, sm, y, x, nx);
+      cta_fence_sync();
+      server_stage<4>(bk, cm, cx, sm, y, x, nx);
+      cta_fence_sync();
+      server_stage<5>(bk, cm, cx, sm, y, x, nx);
+    });
+  } else {
+    SRV(3, sc);
+    sp_barrier(cm, cx, sm);
+    SRV(4, sc);
+    sp_barrier(cm, cx, sm);
+    SRV(5, sc);
+  }
   if (ovf2) {
     SRV(6, sh);
     sp_barrier(cm, cx, sm);
@@ -508,7 +548,8 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
 
 // Ring: N hops of (add the predecessor's pairs, update, select, store into the
 // successor's inbox), the last hop storing into every inbox; then every rank scatters
-// the N reduced chunks.  Three barriers per hop when no candidate list overflows.
+// the N reduced chunks.  Three barriers per hop when the candidate lists are short,
+// five otherwise.
 __global__ void __launch_bounds__(kSpThreads, 3)
 sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   __shared__ SpSmem sm;
@@ -530,13 +571,27 @@ sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
       run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
     sp_barrier(cm, cx, sm);
     const bool ovf = any_overflow(cx.ws + (size_t)hop * nseg * kWsWords, nseg, sm);
-    run_units(cx, nseg, 1, [&](int y, uint32_t x, uint32_t nx) {
-      ring_stage<3>(bk, cm, cx, sm, hop, y, x, nx);
-      cta_fence_sync();
-      ring_stage<4>(bk, cm, cx, sm, hop, y, x, nx);
-      cta_fence_sync();
-      ring_stage<5>(bk, cm, cx, sm, hop, y, x, nx);
-    });
+    if (max_candidates(cx.ws + (size_t)hop * nseg * kWsWords, nseg, sm) <= kSmallCand) {
+      sp_mark(cx, 0);
+      run_units(cx, nseg, 1, [&](int y, uint32_t x, uint32_t nx) {
+        ring_stage<3>(bk, cm, cx, sm, hop, y, x, nx);
+        cta_fence_sync();
+        sp_mark(cx, 1);
+        ring_stage<4>(bk, cm, cx, sm, hop, y, x, nx);
+        cta_fence_sync();
+        sp_mark(cx, 2);
+        ring_stage<5>(bk, cm, cx, sm, hop, y, x, nx);
+        sp_mark(cx, 3);
+      });
+    } else {
+      HOP(3, sc);
+      sp_barrier(cm, cx, sm);
+      HOP(4, sc);
+      sp_barrier(cm, cx, sm);
+      sp_mark(cx, 2);
+      HOP(5, sc);
+      sp_mark(cx, 3);
+    }
     if (ovf) {
       HOP(6, sh);
       sp_barrier(cm, cx, sm);
@@ -547,6 +602,7 @@ sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   }
 #undef HOP
   // gather: rank src finalised chunk src + 1
+  sp_mark(cx, 4);
   const uint32_t units = nseg * (uint32_t)N;
   run_units(cx, units, slices_cap(cx, units, 16), [&](int y, uint32_t x, uint32_t nx) {
     const int src = y % N;

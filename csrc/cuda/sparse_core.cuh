@@ -33,7 +33,7 @@ struct FindSmem {
 
 // Largest bin whose suffix count reaches k.  krem = how many of the k fall in
 // that bin or below the bins above it, i.e. k - count(bins > bin).
-__device__ __forceinline__ void find_bin(const uint32_t* __restrict__ hist, uint32_t k,
+static __device__ __noinline__ void find_bin(const uint32_t* __restrict__ hist, uint32_t k,
                                          FindSmem& fs, uint32_t& bin, uint32_t& krem) {
   constexpr int per = kBins / kSpThreads;  // 16
   uint32_t c[per];
@@ -43,14 +43,26 @@ __device__ __forceinline__ void find_bin(const uint32_t* __restrict__ hist, uint
     c[i] = __ldcg(hist + threadIdx.x * per + i);  // written by other CTAs' atomics: read at L2
     sum += c[i];
   }
-  fs.sums[threadIdx.x] = sum;
+  // above = how many elements sit in the bins of higher threads: suffix sum by warp
+  // shuffles plus the warps' totals (a serial walk over the 256 partial sums cost
+  // several microseconds per call, and a selection makes six calls)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t v = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t y = __shfl_down_sync(0xffffffffu, v, o);
+    if (lane + o < 32) v += y;
+  }
+  if (lane == 0) fs.sums[warp] = v;
   if (threadIdx.x == 0) {
     fs.res[0] = 0;
     fs.res[1] = 0;
   }
   __syncthreads();
-  uint32_t above = 0;
-  for (int t = (int)threadIdx.x + 1; t < kSpThreads; ++t) above += fs.sums[t];
+  uint32_t above = v - sum;
+#pragma unroll
+  for (int w = 0; w < kSpThreads / 32; ++w)
+    if (w > warp) above += fs.sums[w];
   if (above < k && k <= above + sum) {
     uint32_t acc = above;
 #pragma unroll
@@ -99,7 +111,7 @@ __device__ __forceinline__ void st4(float* p, uint64_t i, uint64_t n, bool vec, 
 // MODE 1: GradDrop  a += g
 // MODE 2: DGC       u = m*u + g ; a += u
 template <int MODE>
-__device__ __forceinline__ void pass0_body(const float* __restrict__ g, float* __restrict__ a,
+static __device__ __noinline__ void pass0_body(const float* __restrict__ g, float* __restrict__ a,
                                            float* __restrict__ u, uint64_t n, float momentum,
                                            uint32_t* __restrict__ ws, uint32_t* sh, uint32_t cta,
                                            uint32_t nctas) {
@@ -134,10 +146,12 @@ __device__ __forceinline__ void pass0_body(const float* __restrict__ g, float* _
   flush_hist(sh, ws);
 }
 
-template <int PASS>
-__device__ __forceinline__ void pass_body(const float* __restrict__ a, uint64_t n, uint32_t k,
-                                          uint32_t* __restrict__ ws, uint32_t* sh, FindSmem& fs,
-                                          uint32_t cta, uint32_t nctas) {
+// One copy of the code for both digit passes (PASS is a run-time value) and one per
+// body below: the persistent kernels call every body from several phases, and inlined
+// copies made them so large that cold instruction fetches showed in the phase times.
+static __device__ __noinline__ void pass_body_rt(int PASS, const float* __restrict__ a, uint64_t n,
+                                          uint32_t k, uint32_t* __restrict__ ws, uint32_t* sh,
+                                          FindSmem& fs, uint32_t cta, uint32_t nctas) {
   for (int i = threadIdx.x; i < kBins; i += kSpThreads) sh[i] = 0;
   uint32_t bin0, k1, bin1 = 0, k2;
   find_bin(ws, k, fs, bin0, k1);
@@ -166,6 +180,12 @@ __device__ __forceinline__ void pass_body(const float* __restrict__ a, uint64_t 
   __syncthreads();
   flush_hist(sh, ws + PASS * kBins);
 }
+template <int PASS>
+__device__ __forceinline__ void pass_body(const float* __restrict__ a, uint64_t n, uint32_t k,
+                                          uint32_t* __restrict__ ws, uint32_t* sh, FindSmem& fs,
+                                          uint32_t cta, uint32_t nctas) {
+  pass_body_rt(PASS, a, n, k, ws, sh, fs, cta, nctas);
+}
 
 struct EmitSmem {
   uint32_t warp_tot[kSpThreads / 32];
@@ -186,7 +206,7 @@ struct EmitDst {
 // With `remap` the scanned array `a` is a compacted candidate list: element i stands
 // for element remap[i] of the accumulator a_orig (and of u), which is what gets
 // reported and zeroed.
-__device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float* __restrict__ u,
+static __device__ __noinline__ bool emit_body(int alg, float* __restrict__ a, float* __restrict__ u,
                                           uint64_t n, uint32_t k, uint32_t kmax, const EmitDst& dst,
                                           uint32_t* __restrict__ ws, FindSmem& fs, EmitSmem& es,
                                           uint32_t cta, uint32_t nctas,
@@ -205,17 +225,20 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
 
   const uint64_t tiles = (n + 4095) / 4096;
   for (uint64_t t = cta; t < tiles; t += nctas) {
-    float e[16];
+    // The loops over a thread's 16 elements stay rolled (and the second one loads the
+    // values again, from cache) on purpose: this body runs once or a few times per
+    // launch, so its time is instruction fetch, not arithmetic -- fully unrolled it
+    // took 13 us per tile, most of it waiting for code.
     uint32_t flag = 0;  // 2 bits per element: bit0 greater, bit1 equal
     uint32_t cnt = 0;   // low 16: greater, high 16: equal
-#pragma unroll
+#pragma unroll 1
     for (int j = 0; j < 4; ++j) {
       const uint64_t i = t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4;
       const float4 av = ld4(a, i, n, vec);
-      e[4 * j] = av.x; e[4 * j + 1] = av.y; e[4 * j + 2] = av.z; e[4 * j + 3] = av.w;
+      const float e4[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint32_t key = abs_key(e[4 * j + q]);
+        const uint32_t key = abs_key(e4[q]);
         if (i + q < n) {
           if (key > thr) { flag |= 1u << (2 * (4 * j + q)); cnt += 1u; }
           else if (key == thr && need_eq) { flag |= 2u << (2 * (4 * j + q)); cnt += 1u << 16; }
@@ -257,12 +280,23 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
     const uint32_t base = es.base_gt, acc_eq = es.base_eq;
     uint32_t pg = base + (excl & 0xFFFFu);             // next slot for a "greater" element
     uint32_t rank_eq = excl >> 16;                     // tie rank inside this tile
-#pragma unroll
+    const bool rvec = (reinterpret_cast<uintptr_t>(remap) & 15) == 0;
+#pragma unroll 1
     for (int j = 0; j < 4; ++j) {
+      const uint32_t fj = (flag >> (8 * j)) & 255u;
+      if (fj == 0) continue;
       const uint64_t i = t * 4096 + (uint64_t)(j * kSpThreads + threadIdx.x) * 4;
+      const float4 av = ld4(a, i, n, vec);
+      const float e4[4] = {av.x, av.y, av.z, av.w};
+      uint32_t r4[4] = {0u, 0u, 0u, 0u};
+      if (remap) {  // original indices of a candidate list, fetched four at a time
+        const float4 rv = ld4(reinterpret_cast<const float*>(remap), i, n, rvec);
+        r4[0] = __float_as_uint(rv.x); r4[1] = __float_as_uint(rv.y);
+        r4[2] = __float_as_uint(rv.z); r4[3] = __float_as_uint(rv.w);
+      }
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint32_t f = (flag >> (2 * (4 * j + q))) & 3u;
+        const uint32_t f = (fj >> (2 * q)) & 3u;
         uint32_t pos = 0xFFFFFFFFu;
         if (f & 1u) pos = pg++;
         else if (f & 2u) {
@@ -270,11 +304,11 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
           ++rank_eq;
         }
         if (pos < kmax) {
-          uint32_t where = remap ? remap[i + q] : (uint32_t)(i + q);
+          uint32_t where = remap ? r4[q] : (uint32_t)(i + q);
           if (remap && where >= n_orig) where = 0;  // never index outside the accumulator
           for (int d = 0; d < dst.n; ++d) {
             reinterpret_cast<uint32_t*>(dst.out[d] + 16)[pos] = where;
-            reinterpret_cast<float*>(dst.out[d] + val_off)[pos] = e[4 * j + q];
+            reinterpret_cast<float*>(dst.out[d] + val_off)[pos] = e4[q];
           }
           if (remap) a_orig[where] = 0.0f;
           else a[i + q] = 0.0f;
@@ -287,7 +321,10 @@ __device__ __forceinline__ bool emit_body(int alg, float* __restrict__ a, float*
   // last CTA writes the header
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();  // pairs may sit in a peer's memory
+    // device scope is enough here: the one thread that finds itself last publishes
+    // the unit (header, then a system-scope release of the flag by the caller), and
+    // release is cumulative over what it has observed through this counter
+    __threadfence();
     const uint32_t ticket = atomicAdd(ws + kWsDone, 1u);
     if (ticket == nctas - 1) {
       __threadfence();
@@ -327,7 +364,7 @@ struct SplitSmem {
 // finds in shared memory with plain shared atomics -- no block scan, no barrier
 // per tile -- and reserves its slice of the global lists once at the end.  Finds
 // beyond the shared buffer go to the global lists one by one.
-__device__ __forceinline__ void split_body(float* __restrict__ a, float* __restrict__ u, uint64_t n,
+static __device__ __noinline__ void split_body(float* __restrict__ a, float* __restrict__ u, uint64_t n,
                                            uint32_t k, uint32_t kmax, const EmitDst& dst,
                                            uint32_t* __restrict__ ws, float* __restrict__ cand_val,
                                            uint32_t* __restrict__ cand_idx, uint32_t cand_cap,
@@ -413,7 +450,7 @@ __device__ __forceinline__ void split_body(float* __restrict__ a, float* __restr
 }
 
 // out[idx] (+)= val * scale ; indices come from another rank: bounds-checked
-__device__ __forceinline__ void scatter_body(const uint8_t* __restrict__ payload,
+static __device__ __noinline__ void scatter_body(const uint8_t* __restrict__ payload,
                                              float* __restrict__ out, uint64_t n, uint32_t kmax,
                                              float scale, int accumulate, uint32_t cta,
                                              uint32_t nctas) {

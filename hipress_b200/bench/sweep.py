@@ -91,11 +91,11 @@ def sweep_fused(sizes, iters, ranks, ctas, out):
                 del b, G, Rr, O
 
 
-def run_single(alg, topo, mbytes, ctas, iters, out):
+def run_single(alg, topo, mbytes, ctas, iters, out, flush_l2=True):
     """One rank, one tensor, one fused launch per iteration (the case to hand to
     a profiler): encode + local hand-off + decode of `mbytes` of fp32 gradient."""
     peaks = measured_peaks()
-    flush = L2Flusher()
+    flush = L2Flusher() if flush_l2 else None
     c = Compressor(alg)
     n = mbytes * 1024 * 1024 // 4
     if c.spec.sparse:
@@ -116,7 +116,8 @@ def run_single(alg, topo, mbytes, ctas, iters, out):
         row = {"kernel": f"{topo}_{alg}_1rank", "mbytes": mbytes, "ms": round(t["median_ms"], 5),
                "gbs": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
                "peak_source": peaks["source"],
-               "phase_end_ms": [round(x, 4) for x in b.last_phase_times()]}
+               "phase_end_ms": [round(x, 4) for x in b.last_phase_times()],
+               "marks_ms": [round(x, 4) for x in b.last_marks]}
         out.append(row)
         print(json.dumps(row), flush=True)
         return
@@ -148,6 +149,8 @@ def main(argv=None):
     ap.add_argument("--ranks", type=int, default=8)
     ap.add_argument("--ctas", type=int, default=32, help="CTAs per emulated rank")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--no-flush", action="store_true",
+                    help="--what single: leave L2 (data and code) warm between timed runs")
     a = ap.parse_args(argv)
     sizes = []
     s = a.min_kb * 1024
@@ -156,7 +159,7 @@ def main(argv=None):
         s *= 4
     out = []
     if a.what == "single":
-        run_single(a.alg, a.topo, a.mbytes, a.ctas, a.iters, out)
+        run_single(a.alg, a.topo, a.mbytes, a.ctas, a.iters, out, flush_l2=not a.no_flush)
     if a.what in ("ops", "all"):
         sweep_ops(sizes, a.iters, out)
     if a.what in ("fused", "all"):

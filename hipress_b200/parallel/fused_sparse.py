@@ -119,6 +119,7 @@ class FusedSparseBucket:
         w = self.ws[ctl:ctl + 128].cpu().tolist()
         gen = w[1]
         st = [(x & 0xFFFFFFFF) for x in w[STAMPS:STAMPS + min(gen + 2, 128 - STAMPS)]]
+        self.last_marks = [((x & 0xFFFFFFFF) - st[0]) % (1 << 32) * 1e-6 for x in w[64:72]]
         return [((x - st[0]) & 0xFFFFFFFF) * 1e-6 for x in st[1:]]
 
     def check_status(self):
