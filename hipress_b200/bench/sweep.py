@@ -5,6 +5,7 @@ algorithmic HBM bytes and the fraction of the measured copy bandwidth.
 
     python -m hipress_b200.bench.sweep --what ops --out sweep_ops.json
     python -m hipress_b200.bench.sweep --what fused --ranks 8 --max-mb 256
+    python -m hipress_b200.bench.sweep --what generated --mbytes 256   # CompLL output vs hand kernels
 """
 from __future__ import annotations
 
@@ -137,9 +138,43 @@ def run_single(alg, topo, mbytes, ctas, iters, out, flush_l2=True):
     print(json.dumps(row), flush=True)
 
 
+def sweep_generated(mbytes, iters, out):
+    """Every dense operator generated from the shipped DSL sources (one fused launch
+    per function) against its hand-written twin, on `mbytes` of fp32 gradient."""
+    from ..compll import load_op
+    peaks = measured_peaks()
+    flush = L2Flusher()
+    n = mbytes * 1024 * 1024 // 4
+    g = torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(0)) * 0.02
+    res = torch.empty(n, device="cuda")
+    cases = [("Tbq", "tbq", {}, 4 + (n + 3) // 4, lambda f, r, c: f(g, r, c, 0.01)),
+             ("Onebit", "onebit", {}, 4 + (n + 7) // 8, lambda f, r, c: f(g, r, c)),
+             ("TernGrad", "terngrad", {"bitwidth": 2}, 10 + (n + 3) // 4, lambda f, r, c: f(g, c, 2, seed=1))]
+    for stem, alg, kw, nbytes, call in cases:
+        hand = Compressor(alg, **kw)
+        st = hand.new_state(n, "cuda")
+        pay = torch.empty(hand.payload_bytes(n), dtype=torch.uint8, device="cuda")
+        comp = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        r = torch.zeros(n, device="cuda")
+        enc, dec, acc = load_op(f"{stem}Encode"), load_op(f"{stem}Decode"), load_op(f"{stem}DecodeAccumulate")
+        ops = [("encode", lambda: call(enc, r, comp), lambda: hand.encode(g, st, out=pay)),
+               ("decode", lambda: dec(comp, res), lambda: hand.decode(pay, res)),
+               ("decode_accumulate", lambda: acc(comp, res, 0.5),
+                lambda: hand.decode(pay, res, scale=0.5, accumulate=True))]
+        for op, gen_fn, hand_fn in ops:
+            tg = time_cuda(gen_fn, iters=iters, flush=flush)
+            th = time_cuda(hand_fn, iters=iters, flush=flush)
+            row = {"operator": f"{stem}{op.title().replace('_', '')}", "mbytes": mbytes,
+                   "generated_ms": round(tg["median_ms"], 5), "hand_ms": round(th["median_ms"], 5),
+                   "generated_over_hand": round(tg["median_ms"] / th["median_ms"], 3),
+                   "peak_source": peaks["source"]}
+            out.append(row)
+            print(json.dumps(row), flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", choices=["ops", "fused", "single", "all"], default="all")
+    ap.add_argument("--what", choices=["ops", "fused", "single", "generated", "all"], default="all")
     ap.add_argument("--alg", default="tbq")
     ap.add_argument("--topo", default="ring")
     ap.add_argument("--mbytes", type=int, default=256)
@@ -160,6 +195,8 @@ def main(argv=None):
     out = []
     if a.what == "single":
         run_single(a.alg, a.topo, a.mbytes, a.ctas, a.iters, out, flush_l2=not a.no_flush)
+    if a.what == "generated":
+        sweep_generated(a.mbytes, a.iters, out)
     if a.what in ("ops", "all"):
         sweep_ops(sizes, a.iters, out)
     if a.what in ("fused", "all"):

@@ -241,6 +241,11 @@ class Emitter:
             s = self.syms.get(e.base.id)
             if s is None or s.kind not in ("param_vector", "vector"):
                 raise CompileError(f"{e.base.id} is not a vector")
+            hook = getattr(self, "_index_hook", None)
+            if hook is not None:      # fused target: the element at the own index lives in a register
+                got = hook(s, e.idx, local)
+                if got is not None:
+                    return got
             i = X(e.idx)
             if s.bits is not None:
                 b = self.expr(s.bits, set(), ctx)
@@ -249,6 +254,9 @@ class Emitter:
         if isinstance(e, F.Random):
             site = self.rand_sites
             self.rand_sites += 1
+            hook = getattr(self, "_random_hook", None)
+            if hook is not None:      # fused target: one Philox call serves four elements
+                return f"({X(e.lo)} + ({X(e.hi)} - {X(e.lo)}) * {hook(site)})"
             return (f"({X(e.lo)} + ({X(e.hi)} - {X(e.lo)}) * "
                     f"compll_rand01(c.seed, (uint64_t)l_{self._counter}, {site}u))")
         raise CompileError(f"expression not supported here: {type(e).__name__}")
@@ -271,7 +279,11 @@ class Emitter:
                     out.append(self.stmts(st.other, set(local), ret_partial, indent + "  "))
                 out.append(f"{indent}}}")
             elif isinstance(st, F.Return):
-                out.append(f"{indent}return {self.expr(st.value, local)};")
+                rv = getattr(self, "_return_to", None)
+                if rv is not None:    # inlined lambda: the caller wraps the body in do { } while (0)
+                    out.append(f"{indent}{{ {rv} = {self.expr(st.value, local)}; break; }}")
+                else:
+                    out.append(f"{indent}return {self.expr(st.value, local)};")
             elif isinstance(st, F.ExprStmt):
                 out.append(f"{indent}{self.expr(st.value, local)};")
             else:
@@ -516,10 +528,18 @@ __global__ void __launch_bounds__(256) {name}_map{idx}_kernel({self.kernel_param
         name = self.fn.name
         self.rand_sites = 0  # call sites are numbered per emission: both targets agree
         lambdas = "\n".join(self.lambda_fn(s) for s in self.syms.values() if s.kind == "lambda")
-        maps = "\n".join(self.map_kernel(i, t, m, i == len(self.maps) - 1)
-                         for i, (t, m) in enumerate(self.maps))
-        reduces = "\n".join(self.reduce_kernel(gi, st[1]) for gi, st in enumerate(self.stages)
-                            if st[0] == "reduce")
+        fused = self.fused_plan()
+        if fused is not None:
+            # one persistent kernel for the whole function (emit_fused.py); the random
+            # call sites are numbered as the staged kernels and the CPU target number them
+            from .emit_fused import FusedGen
+            self.rand_sites = 0
+            maps, reduces = FusedGen(fused).kernel_source(), ""
+        else:
+            maps = "\n".join(self.map_kernel(i, t, m, i == len(self.maps) - 1)
+                             for i, (t, m) in enumerate(self.maps))
+            reduces = "\n".join(self.reduce_kernel(gi, st[1]) for gi, st in enumerate(self.stages)
+                                if st[0] == "reduce")
         src_comment = "\n".join("//   " + l for l in self.fn.source.strip().splitlines())
         return f"""// Generated by hipress_b200.compll from the DSL function {name}:
 //
@@ -540,6 +560,17 @@ namespace compll_gen_{name} {{
 {maps}
 }}  // namespace compll_gen_{name}
 """
+
+    def fused_plan(self):
+        """The one-launch plan of this function, or None when it keeps one kernel per
+        stage (library-lowered stages, lambdas calling lambdas; ``fuse=False``)."""
+        if not getattr(self, "fuse", True):
+            return None
+        if not hasattr(self, "_fused_plan"):
+            from .emit_fused import FusedPlan
+            plan = FusedPlan(self)
+            self._fused_plan = plan if plan.ok else None
+        return self._fused_plan
 
     def wrapper_source(self) -> str:
         """``extern "C"`` launcher (``-w``): stream-ordered, no host synchronisation."""
@@ -603,6 +634,9 @@ namespace compll_gen_{name} {{
             else:
                 rows.append(f"  compll_gen_{name}::{name}_map{st[1]}_kernel<<<grid, 256, 0, st>>>"
                             f"({self.kernel_args()});")
+        if self.fused_plan() is not None:
+            from .emit_fused import FusedGen
+            rows = [FusedGen(self.fused_plan()).launch_rows()]
         red = f"""  float* partials = scalars + 16;
   unsigned int* ticket = reinterpret_cast<unsigned int*>(scalars + 16 + {max(nred, 1)} * kMaxBlocks);
   (void)partials; (void)ticket;
@@ -733,5 +767,8 @@ def {name}({", ".join(args)}, seed=0, stream=None):
 '''
 
 
-def generate(src: str) -> Emitter:
-    return Emitter(F.parse(src))
+def generate(src: str, fuse: bool = True) -> Emitter:
+    """``fuse=False`` keeps one kernel per reduce group / map (the staged target)."""
+    em = Emitter(F.parse(src))
+    em.fuse = fuse
+    return em
