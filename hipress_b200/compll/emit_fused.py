@@ -218,6 +218,7 @@ class FusedGen:
     def _phase(self, pi: int, ph: Phase, last: bool) -> str:
         em = self.em
         need_in: dict[str, None] = {}
+        need_frag: dict[str, None] = {}
         sites: list[int] = []
         fwd: dict[str, str] = {}
         body = []
@@ -232,7 +233,13 @@ class FusedGen:
             if sym.bits is None:
                 need_in[sym.name] = None
                 return f"in_{sym.name}[e]"
-            return None
+            return frag_value(sym)
+
+        def frag_value(sym):
+            # a packed input read at the own index: the group's fragment is loaded once
+            need_frag[sym.name] = None
+            b = f"(uint32_t)({em.expr(sym.bits, set())})"
+            return f"((fr_{sym.name} >> (e * {b})) & ((1u << {b}) - 1u))"
 
         def random_hook(site):
             sites.append(site)
@@ -245,7 +252,7 @@ class FusedGen:
             if s.bits is None:
                 need_in[vec] = None
                 return f"in_{vec}[e]"
-            return f"compll_get_bits(c.v_{vec}, i, (uint32_t)({em.expr(s.bits, set())}))"
+            return frag_value(s)
 
         em._index_hook, em._random_hook = index_hook, random_hook
         decls, stores = [], []
@@ -305,6 +312,9 @@ class FusedGen:
             em._return_to = None
         loads = [f"      {C_TYPES[em.syms[v].type.name]} in_{v}[4];\n"
                  f"      compll_load4(c.v_{v}, i0, count, in_{v});" for v in need_in]
+        for v in need_frag:
+            b = f"(uint32_t)({em.expr(em.syms[v].bits, set())})"
+            loads.append(f"      const uint32_t fr_{v} = compll_load_frag(c.v_{v}, (c.n_{v} * {b} + 7) / 8, q, {b});")
         rngs = [f"      const hipress::Philox4 rg{s} = compll_rand4(c.seed, q, {s}u);" for s in sorted(set(sites))]
         reds = [it.sym for it in ph.items if it.kind == "reduce"]
         acc_init = [f"    {C_TYPES[s.type.name]} acc_{s.name} = ({C_TYPES[s.type.name]})"
