@@ -50,6 +50,8 @@ struct BucketDev {
   int nseg;
   uint32_t tiles_total;  // tiles of one chunk summed over segments = work items of a phase
   uint64_t slot_bytes;
+  uint64_t inbox_bytes;  // slot_bytes * slots of the topology: what a rank's inbox holds
+  uint64_t dbg_limit;    // debug build: pretend the inbox ends here (0: at inbox_bytes)
 };
 
 // The decode phases take their tiles in groups of kGroup: the payload loads of a
@@ -157,6 +159,26 @@ __device__ __forceinline__ void unpack_words(const uint32_t (&w)[LL<B>::W], uint
 template <int ALG, int B>
 __device__ __forceinline__ uint2* tile_base(uint8_t* base, uint32_t t) {
   return reinterpret_cast<uint2*>(base) + (size_t)t * tile_slots<ALG, B>();
+}
+
+// Debug build (-DHIPRESS_DEBUG): every tile of payload slots a kernel is about to
+// store into or poll is checked against the inbox it belongs to.  A tile outside it
+// is recorded in the status word (HP_STATUS_BOUNDS | what) and skipped -- never
+// touched.  In the normal build the check folds to `true`.
+template <int ALG, int B>
+__device__ __forceinline__ bool dbg_tile_ok(const BucketDev& bk, const void* inbox,
+                                            const uint8_t* payload, uint32_t t, uint32_t* status,
+                                            uint32_t what) {
+#ifdef HIPRESS_DEBUG
+  const uint8_t* lo = static_cast<const uint8_t*>(inbox);
+  const uint64_t limit = bk.dbg_limit ? bk.dbg_limit : bk.inbox_bytes;
+  const uint64_t end = (uint64_t)(payload - lo) + (uint64_t)(t + 1) * tile_slots<ALG, B>() * 8ull;
+  if (payload < lo || end > limit) {
+    atomicCAS(status, 0u, HP_STATUS_BOUNDS | what);
+    return false;
+  }
+#endif
+  return true;
 }
 
 // send one encoded tile: this thread's code words, and (thread 0) the metadata
@@ -416,7 +438,9 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
       float x[kIter][4];
       // first loads of the incoming payload go out before anything waits
       TileRx<ALG, B> rx;
-      if (in_base) recv_issue<ALG, B>(in_base + sg.pay_off, t, rx);
+      const bool has_in = in_base && dbg_tile_ok<ALG, B>(bk, my_inbox, in_base + sg.pay_off, t, status, 1u);
+      if (in_base && !has_in) sm.ws.poisoned = 1;
+      if (has_in) recv_issue<ALG, B>(in_base + sg.pay_off, t, rx);
       const bool bulk = bulk_ok(gp, rp, m);
       int st = 0;
       if (bulk) {
@@ -430,7 +454,7 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
       } else {
         load_tile(gp, m, x);
       }
-      if (in_base) {
+      if (has_in) {
         float d[kIter][4];
         recv_finish<ALG, B>(in_base + sg.pay_off, t, rx, cm, status,
                             HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
@@ -461,7 +485,9 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
       const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
 #pragma unroll
       for (int q = 0; q < HP_MAX_RANKS; ++q)
-        if (q < ps.ndst) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
+        if (q < ps.ndst && dbg_tile_ok<ALG, B>(bk, cm.inbox[(ps.dst0 + q) % N], dst_base[q] + sg.pay_off,
+                                               t, status, 2u))
+          send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
       __syncthreads();  // the prefetch stage of this tile may be refilled from here on
     }
     trace_phase(cm, E, ph, sm.ws);
@@ -491,7 +517,12 @@ __device__ __forceinline__ void decode_phase(const BucketDev& bk, const HpComm& 
       if (more) {
         more = cursor_next(bk, G, b, cur, tr[u]);
         if (more) {
-          recv_issue<ALG, B>(sp + bk.seg[tr[u].seg].pay_off, tr[u].t, rx[u]);
+          if (dbg_tile_ok<ALG, B>(bk, cm.inbox[R], sp + bk.seg[tr[u].seg].pay_off, tr[u].t, status, 3u)) {
+            recv_issue<ALG, B>(sp + bk.seg[tr[u].seg].pay_off, tr[u].t, rx[u]);
+          } else {
+            sm.ws.poisoned = 1;   // ll_finish returns at once, nothing is stored
+            rx[u] = TileRx<ALG, B>();
+          }
           cnt = u + 1;
         }
       }
@@ -588,6 +619,11 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
       // the N pushes are polled two at a time: loads of the next source are in
       // flight while the current one is decoded
       TileRx<ALG, B> rx[2];
+      if (!dbg_tile_ok<ALG, B>(bk, my_inbox, my_inbox + (size_t)(N - 1) * bk.slot_bytes + sg.pay_off, t,
+                               status, 4u)) {
+        sm.ws.poisoned = 1;
+        continue;
+      }
       recv_issue<ALG, B>(my_inbox + sg.pay_off, t, rx[0]);
       for (int q = 0; q < N; ++q) {
         if (q + 1 < N)
@@ -621,7 +657,8 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
       const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
 #pragma unroll
       for (int q = 0; q < HP_MAX_RANKS; ++q)
-        if (q < N) send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
+        if (q < N && dbg_tile_ok<ALG, B>(bk, cm.inbox[(R + q) % N], dst_base[q] + sg.pay_off, t, status, 5u))
+          send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
     }
     trace_phase(cm, E, N, sm.ws);
   }
@@ -667,6 +704,8 @@ static int build_bucket(int alg, int bits, const HpSeg* segs, int nseg, int nran
   bk.nseg = nseg;
   bk.tiles_total = (uint32_t)tiles;
   bk.slot_bytes = pay;
+  bk.inbox_bytes = 0;
+  bk.dbg_limit = 0;
   return 0;
 }
 
@@ -721,7 +760,32 @@ static int launch_fused(int topo, const BucketDev& bk, const HpComm& cm, const F
 
 using namespace hipress;
 
+// debug build: see hp_cuda_debug_set_inbox_limit
+static uint64_t g_dbg_inbox_limit = 0;
+
 extern "C" {
+
+// 1 when the library was built with -DHIPRESS_DEBUG (per-access bounds checks on)
+int hp_cuda_debug_build(void) {
+#ifdef HIPRESS_DEBUG
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Debug build only: make the kernels' bounds checks treat every inbox as `bytes`
+// long (0: its real size), so a test can make the checks fire without any access
+// actually leaving the allocation.  Returns HP_ERR_BAD_ARG in the normal build.
+int hp_cuda_debug_set_inbox_limit(uint64_t bytes) {
+#ifdef HIPRESS_DEBUG
+  g_dbg_inbox_limit = bytes;
+  return 0;
+#else
+  (void)bytes;
+  return HP_ERR_BAD_ARG;
+#endif
+}
 
 // bytes of one rank's inbox for a bucket of tensors with the given sizes
 int hp_fused_dense_layout(int topo, int alg, int bits, const uint64_t* ns, int nseg, int nranks,
@@ -751,6 +815,8 @@ int hp_cuda_fused_dense(int topo, int alg, int bits, const HpSeg* segs, int nseg
   BucketDev bk;
   int rc = build_bucket(alg, bits, segs, nseg, comm->nranks, bk);
   if (rc) return rc;
+  bk.inbox_bytes = bk.slot_bytes * (uint64_t)num_slots(topo, comm->nranks);
+  bk.dbg_limit = g_dbg_inbox_limit;
   {  // never more CTAs than work items
     const uint64_t items = (uint64_t)bk.tiles_total * (uint64_t)num_phases(topo, comm->nranks);
     if ((uint64_t)ctas > items) ctas = (int)items;

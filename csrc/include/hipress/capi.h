@@ -24,6 +24,7 @@
 // status words written by a kernel whose bounded wait expired
 #define HP_STATUS_OK 0u
 #define HP_STATUS_TIMEOUT 0x80000000u  // | (phase << 16) | (slot << 8) | cta
+#define HP_STATUS_BOUNDS 0x20000000u    // debug build: an index left its buffer (recorded, skipped) | site
 #define HP_STATUS_UPSTREAM 0x40000000u  // or-ed in: the sender of this input had given up first
 
 #ifdef __cplusplus

@@ -61,6 +61,39 @@ def nvcc_path() -> str | None:
     return None
 
 
+def build_debug(force: bool = False, verbose: bool = False):
+    """The CUDA library once more with ``-DHIPRESS_DEBUG``: the kernels check every
+    payload-slot index against its inbox, record a violation in the status word and
+    skip the access (what stands in for compute-sanitizer where that tool is not
+    available).  Loaded instead of the normal library when HIPRESS_DEBUG=1."""
+    nv = nvcc_path()
+    if nv is None:
+        return None
+    _, cuda_src = _sources()
+    obj = OBJ / "debug"
+    obj.mkdir(parents=True, exist_ok=True)
+    out = HERE / "libhipress_cuda_debug.so"
+    stamp = obj / "cuda.sha"
+    dg = _digest(cuda_src) + "-debug"
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == dg:
+        return out
+    inc = ["-I", str(CSRC / "include"), "-I", str(CSRC / "cuda")]
+    with open(OBJ / "build.log", "a") as log:
+        objs = [obj / (s.stem + ".o") for s in cuda_src]
+
+        def one(pair):
+            s, o = pair
+            return _run([nv, *NVCC_FLAGS, "-DHIPRESS_DEBUG", *inc, "-c", str(s), "-o", str(o)], log)
+
+        with ThreadPoolExecutor(max_workers=min(8, len(cuda_src))) as ex:
+            list(ex.map(one, zip(cuda_src, objs)))
+        _run([nv, "-shared", "-o", str(out), *map(str, objs), "-lcudart"], log)
+    stamp.write_text(dg)
+    if verbose:
+        print("built", out)
+    return out
+
+
 def build(force: bool = False, verbose: bool = False) -> dict:
     """Compile whatever is out of date; returns the paths of the libraries."""
     cpu_src, cuda_src = _sources()
@@ -100,6 +133,8 @@ def build(force: bool = False, verbose: bool = False) -> dict:
 
 def main():
     print(build(force="--force" in sys.argv, verbose=True))
+    if "--debug" in sys.argv:
+        print(build_debug(force="--force" in sys.argv, verbose=True))
 
 
 if __name__ == "__main__":

@@ -108,7 +108,15 @@ def cuda():
         return _cuda
     path = HERE / "libhipress_cuda.so"
     err = None
-    if not path.exists() or os.environ.get("HIPRESS_REBUILD"):
+    if os.environ.get("HIPRESS_DEBUG", "0") not in ("", "0"):
+        # the build with per-access bounds checks in the kernels (-DHIPRESS_DEBUG)
+        from . import build as _b
+        path = HERE / "libhipress_cuda_debug.so"
+        try:
+            _b.build_debug()
+        except Exception as e:  # noqa: BLE001
+            err = e
+    elif not path.exists() or os.environ.get("HIPRESS_REBUILD"):
         err = _ensure_built()
     if not path.exists():
         raise NativeLibraryError(
@@ -124,6 +132,8 @@ def cuda():
     _sig(L.hp_fused_dense_layout, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_uint64),
          C.c_int, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32))
     _sig(L.hp_fused_chunk_elems, C.c_uint64, C.c_uint64, C.c_int)
+    _sig(L.hp_cuda_debug_build, C.c_int)
+    _sig(L.hp_cuda_debug_set_inbox_limit, C.c_int, C.c_uint64)
     _sig(L.hp_cuda_fused_dense, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(HpSeg), C.c_int,
          C.POINTER(HpComm), C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, vp)
     _sig(L.hp_sparse_workspace_bytes, C.c_uint64)

@@ -29,6 +29,8 @@ class HipressTimeoutError(RuntimeError):
 def decode_status(word: int) -> str:
     if word == 0:
         return "ok"
+    if word & 0x20000000 and not word & 0x80000000:
+        return f"debug build: a payload index left its inbox at site {word & 0xFFFF} (recorded and skipped)"
     phase = (word >> 16) & 0x3FFF
     slot = (word >> 8) & 0xFF
     cta = word & 0xFF
