@@ -116,7 +116,7 @@ def fit_table(xs, ys) -> TableCost:
     return TableCost(tuple(sorted(best.items())))
 
 
-def profile_from_sweep(path, algorithm="tbq", ops_path=None, fit="table") -> CostProfile:
+def profile_from_sweep(path, algorithm="tbq", ops_path=None, fit="table", p2p_path=None) -> CostProfile:
     """Fit a profile from the rows a multi-GPU run of
     ``hipress_b200.bench.sweep_multi`` wrote (fused ring / PS and NCCL all-reduce
     times per size, measured on real ranks).  ``ops_path``: rows of
@@ -136,6 +136,11 @@ def profile_from_sweep(path, algorithm="tbq", ops_path=None, fit="table") -> Cos
         return fn([p[0] for p in pts], [p[1] for p in pts]) if pts else None
 
     send = LinearCost(4.0 / 770e9 * 1e3, 0.003, 0.003)
+    send_note = ""
+    if p2p_path:   # rows of hipress_b200.bench.p2p: stores issued by a kernel into a peer's memory
+        pr = json.load(open(p2p_path))
+        send = fit_linear([r["bytes"] / 4.0 for r in pr], [r["ms"] for r in pr])
+        send_note = ", send term from the in-kernel peer-store bench"
     enc = LinearCost(1.65e-9, 0.0208, 0.0196)   # stand-alone TBQ kernels, one B200 (profile())
     dec = LinearCost(1.26e-9, 0.0178, 0.0183)
     note = ""
@@ -152,7 +157,7 @@ def profile_from_sweep(path, algorithm="tbq", ops_path=None, fit="table") -> Cos
                        comp_ratio=ratio, fused_ring=term("fused_ms", "ring"),
                        fused_ps=term("fused_ms", "ps"), allreduce=term("allreduce_ms"), margin=MARGIN,
                        min_compress_elems=n * TILE,
-                       source=f"fitted from {n}-GPU sweep rows ({algorithm}){note}")
+                       source=f"fitted from {n}-GPU sweep rows ({algorithm}){note}{send_note}")
 
 
 def main(argv=None):
@@ -161,6 +166,9 @@ def main(argv=None):
                     help="fit from a sweep_multi JSON instead of measuring now")
     ap.add_argument("--from-ops-sweep", default=None,
                     help="with --from-sweep: kernel sweep JSON for the encode / decode terms")
+    ap.add_argument("--from-p2p", default=None,
+                    help="with --from-sweep: rows of hipress_b200.bench.p2p for the send term "
+                         "(default: the 770 GB/s peer-copy figure)")
     ap.add_argument("--fit", default="table", choices=["table", "linear"],
                     help="with --from-sweep: keep the measured points (interpolated) or fit one line")
     ap.add_argument("--algorithm", default="tbq")
@@ -172,7 +180,7 @@ def main(argv=None):
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args(argv)
     if a.from_sweep:
-        prof = profile_from_sweep(a.from_sweep, a.algorithm, a.from_ops_sweep, a.fit)
+        prof = profile_from_sweep(a.from_sweep, a.algorithm, a.from_ops_sweep, a.fit, a.from_p2p)
         with open(a.output, "w") as f:
             f.write(prof.to_json())
         print(a.output)

@@ -133,3 +133,95 @@ def test_ddp_hook_runs_the_fused_kernels_and_matches_the_optimizer(alg, topo):
         assert torch.equal(r["ddp"], r["opt"]), (alg, topo)
         assert torch.equal(r["ddp"], res[0]["ddp"])
         assert torch.equal(r["fa"], res[0]["fa"]) and float(r["fa"].abs().max()) > 0
+
+
+def _elastic_gpu_worker(rank, world, port2, outdir, leave):
+    from hipress_b200.train import pytorch_imagenet as T
+    return T.main(["--model", "bert_tiny", "--batch-size", "2", "--seq-len", "16", "--num-iterations", "6",
+                   "--fp32", "--algorithm", "tbq", "--comp-threshold", "1000", "--threshold", "0.0001",
+                   "--heartbeat-timeout", "1.0", "--elastic", "--elastic-port", str(port2),
+                   "--inject-leave", leave, "--metrics", f"{outdir}/m{rank}.jsonl"])
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", [2, 3])
+def test_training_continues_on_gpus_after_a_rank_leaves(tmp_path, world):
+    """Fused backend, real GPUs: the last rank leaves between two steps (announced on
+    the host, nothing of it in flight); the survivors notice before their next launch,
+    release the symmetric memory of the old membership without any collective (the
+    group it was built on is gone), re-form -- down to a single rank when two become
+    one -- and finish the epoch.  NVLS is off and the kernels use plain peer stores."""
+    import json
+    from _mp import free_port
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = {"NCCL_NVLS_ENABLE": "0", "HIPRESS_PG_TIMEOUT_S": "60"}
+    res = spawn(_elastic_gpu_worker, world, free_port(), str(tmp_path), f"{world - 1}:3", backend="nccl", env=env)
+    assert res == [0] * world
+    recs = [json.loads(r) for r in (tmp_path / "m0.jsonl").read_text().splitlines()]
+    assert recs[-1]["step"] == 6 and recs[-1]["ranks"] == world - 1
+    assert recs[-1]["loss"] == recs[-1]["loss"]
+
+
+def _hier_worker(rank, world, alg, topo, steps):
+    """One box posing as two machines (HIPRESS_NODE_SIZE): fused kernels inside a
+    machine, compressed exchange of shards between machines, all-gather inside."""
+    import hipress_b200 as hp
+    dev = hp.device()
+    sizes = [300001, 5000]
+    params = [torch.nn.Parameter(torch.zeros(s, device=dev)) for s in sizes]
+    opt = hp.DistributedOptimizer(torch.optim.SGD(params, lr=1.0), [("big", params[0]), ("small", params[1])],
+                                  algorithm=alg, topology=topo, comp_threshold=100000, ctas=16,
+                                  timeout_s=5.0, threshold=0.002)
+    eng = opt.engine
+    outs = []
+    for step in range(steps):
+        g = torch.Generator().manual_seed(31 * step + rank)
+        grads = [torch.randn(s, generator=g) * 0.02 for s in sizes]
+        for p, x in zip(params, grads):
+            p.grad = x.to(dev)
+        opt.synchronize()
+        opt._synchronized = False
+        torch.cuda.synchronize()
+        outs.append([p.grad.cpu() for p in params])
+    eng.check()
+    sd = opt.state_dict()["compressor_state"]
+    res = {"outs": outs, "state": sd, "backend": eng.backend, "N": eng.N, "world": eng.world,
+           "hier": eng.outer is not None and (eng.outer["nodes"], eng.outer["local"])}
+    opt.close()
+    return res
+
+
+def test_one_box_split_in_two_machines_runs_hierarchically():
+    from hipress_b200.parallel.simulate import chunk_range
+    world = 8 if torch.cuda.device_count() >= 8 else 4
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    per, steps = world // 2, 4
+    res = spawn(_hier_worker, world, "tbq", "ring", steps, backend="nccl",
+                env={"HIPRESS_NODE_SIZE": str(per), "NCCL_NVLS_ENABLE": "0"})
+    assert all(r["hier"] == (2, per) and r["N"] == per and r["world"] == world and r["backend"] == "fused"
+               for r in res)
+    for r in res[1:]:
+        for s in range(steps):
+            for a, b in zip(r["outs"][s], res[0]["outs"][s]):
+                assert torch.equal(a, b), "replicas differ"
+    sizes = [300001, 5000]
+    def grads(rank, step):
+        g = torch.Generator().manual_seed(31 * step + rank)
+        return [torch.randn(s, generator=g) * 0.02 for s in sizes]
+    for s in range(steps):                                  # uncompressed tensor: exact mean over the job
+        want = sum(grads(r, s)[1] for r in range(world)) / world
+        assert torch.allclose(res[0]["outs"][s][1], want, atol=1e-7)
+    # conservation over both levels: delivered + residuals inside the machines + residuals of
+    # the exchange between machines == exact mean
+    n = sizes[0]
+    delivered = sum(res[0]["outs"][s][0] for s in range(steps))
+    exact = sum(sum(grads(r, s)[0] for r in range(world)) / world for s in range(steps))
+    inner = sum(r["state"]["tensors"]["big"]["residual"] for r in res) / world
+    outer = torch.zeros(n)
+    for q, r in enumerate(res):
+        lo, hi = chunk_range(n, per, q % per)
+        outer[lo:hi] += r["state"]["between_machines"]["big.0"]["residual"] / 2
+    assert torch.allclose(delivered + inner + outer, exact, atol=2e-6)
+    assert not torch.allclose(delivered, exact, atol=1e-4)
