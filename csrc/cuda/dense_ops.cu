@@ -13,7 +13,7 @@
 namespace hipress {
 
 template <int ALG, int B>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 dense_encode_kernel(const float* __restrict__ g, float* __restrict__ r,
                     const uint8_t* __restrict__ in_payload, uint8_t* __restrict__ out,
                     uint32_t n, DenseParams P, uint32_t tensor_id, uint64_t elem_offset) {

@@ -194,9 +194,8 @@ __device__ __forceinline__ void push_stage(const SpBucket& bk, const HpComm& cm,
   bool last = false;
   if (STAGE == 0) {
     if (len == 0) return;
-    float* zo = sg.out + E * cm.emu_stride_out + off;   // the result is cleared behind the read of g
-    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx, zo);
-    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx, zo);
+    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
+    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
     return;
   } else if (STAGE == 1) {
     if (len == 0) return;
@@ -307,8 +306,22 @@ __device__ __forceinline__ void server_stage(const SpBucket& bk, const HpComm& c
 }
 
 // ---------------------------------------------------------------- pull
+// zero-fill of the result (unit y = seg).  It runs one phase after the update pass has
+// read the gradient (which may be the same buffer): clearing each element right behind
+// its load in that pass made the pass five times slower when the buffers were the same
+// (a store to a line whose fill is still in flight).
+__device__ __forceinline__ void zero_stage(const SpBucket& bk, const HpComm& cm, const SpCtx& cx,
+                                           int y, uint32_t x, uint32_t nx) {
+  const SpSeg& sg = bk.seg[y];
+  float* out = sg.out + cx.E * cm.emu_stride_out;
+  const bool vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const uint64_t stride = (uint64_t)nx * kSpThreads * 4;
+  for (uint64_t i = ((uint64_t)x * kSpThreads + threadIdx.x) * 4; i < sg.n; i += stride)
+    st4(out, i, sg.n, vec, make_float4(0.f, 0.f, 0.f, 0.f));
+}
+
 // wait for the reduced chunk c that arrives in inbox slot `slot` and scatter value / N
-// into the result (cleared by the update pass, behind its read of the gradient); unit y = seg * N + j.  A CTA that has given up leaves
+// into the (zero-filled) result; unit y = seg * N + j.  A CTA that has given up leaves
 // the result alone.
 __device__ __forceinline__ void gather_stage(const SpBucket& bk, const HpComm& cm, const SpCtx& cx,
                                              SpSmem& sm, int si, int slot, int c, uint32_t phase,
@@ -373,9 +386,8 @@ __device__ __forceinline__ void ring_stage(const SpBucket& bk, const HpComm& cm,
     return;
   } else if (STAGE == 1) {
     if (len == 0) return;
-    float* zo = sg.out + E * cm.emu_stride_out + off;   // the result is cleared behind the read of g
-    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx, zo);
-    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx, zo);
+    if (bk.alg == kDgc) pass0_body<2>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
+    else pass0_body<1>(g, a, u, len, bk.momentum, ws, sm.sh, x, nx);
     return;
   } else if (STAGE == 2) {
     if (len == 0) return;
@@ -470,6 +482,8 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   PUSH(0, ph);
   sp_barrier(cm, cx, sm);
   PUSH(1, ph);
+  // the gradient has been read (it may be the result buffer): clear the result
+  run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
   sp_barrier(cm, cx, sm);
   const bool ovf = any_overflow(cx.ws, units, sm);
   // the candidate list of a unit is short (about as many pairs as are sent): one CTA
@@ -556,6 +570,8 @@ sp_ring_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
     HOP(1, sh);
     sp_barrier(cm, cx, sm);
     HOP(2, sh);
+    if (hop == N - 1)  // every chunk of the gradient has been read: clear the result
+      run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
     sp_barrier(cm, cx, sm);
     const bool ovf = any_overflow(cx.ws + (size_t)hop * nseg * kWsWords, nseg, sm);
     if (max_candidates(cx.ws + (size_t)hop * nseg * kWsWords, nseg, sm) <= kSmallCand) {

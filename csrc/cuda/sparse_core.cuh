@@ -111,28 +111,23 @@ __device__ __forceinline__ void st4(float* p, uint64_t i, uint64_t n, bool vec, 
 // MODE 1: GradDrop  a += g
 // MODE 2: DGC       u = m*u + g ; a += u
 template <int MODE>
-static __device__ __noinline__ void pass0_body(const float* g, float* __restrict__ a,
+static __device__ __noinline__ void pass0_body(const float* __restrict__ g, float* __restrict__ a,
                                            float* __restrict__ u, uint64_t n, float momentum,
                                            uint32_t* __restrict__ ws, uint32_t* sh, uint32_t cta,
-                                           uint32_t nctas, float* zero_out = nullptr) {
-  // zero_out: the result buffer of a fused synchronisation (it may BE g), cleared here
-  // behind the read of g so that no separate pass over it is needed
+                                           uint32_t nctas) {
   for (int i = threadIdx.x; i < kBins; i += kSpThreads) sh[i] = 0;
   __syncthreads();
   const bool vec = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(g) |
                      reinterpret_cast<uintptr_t>(u)) & 15) == 0;
-  const bool zvec = (reinterpret_cast<uintptr_t>(zero_out) & 15) == 0;
   const uint64_t stride = (uint64_t)nctas * kSpThreads * 4;
   for (uint64_t i = ((uint64_t)cta * kSpThreads + threadIdx.x) * 4; i < n; i += stride) {
     float4 av = ld4(a, i, n, vec);
     if (MODE == 1) {
       const float4 gv = ld4(g, i, n, vec);
-      if (zero_out) st4(zero_out, i, n, zvec, make_float4(0.f, 0.f, 0.f, 0.f));
       av.x = av.x + gv.x; av.y = av.y + gv.y; av.z = av.z + gv.z; av.w = av.w + gv.w;
       st4(a, i, n, vec, av);
     } else if (MODE == 2) {
       const float4 gv = ld4(g, i, n, vec);
-      if (zero_out) st4(zero_out, i, n, zvec, make_float4(0.f, 0.f, 0.f, 0.f));
       float4 uv = ld4(u, i, n, vec);
       uv.x = __fmaf_rn(momentum, uv.x, gv.x);
       uv.y = __fmaf_rn(momentum, uv.y, gv.y);

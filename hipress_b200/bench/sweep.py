@@ -92,7 +92,7 @@ def sweep_fused(sizes, iters, ranks, ctas, out):
                 del b, G, Rr, O
 
 
-def run_single(alg, topo, mbytes, ctas, iters, out, flush_l2=True):
+def run_single(alg, topo, mbytes, ctas, iters, out, flush_l2=True, in_place=False):
     """One rank, one tensor, one fused launch per iteration (the case to hand to
     a profiler): encode + local hand-off + decode of `mbytes` of fp32 gradient."""
     peaks = measured_peaks()
@@ -106,7 +106,7 @@ def run_single(alg, topo, mbytes, ctas, iters, out, flush_l2=True):
         st = c.new_state(n, "cuda")
         acc = st["accum_v"] if "accum_v" in st else st["residual"]
         u = st.get("momentum_u")
-        o = torch.empty(n, device="cuda")
+        o = g if in_place else torch.empty(n, device="cuda")   # the engine synchronises in place
         sr = torch.zeros(b.chunk_elems(0), device="cuda")
         t = time_cuda(lambda: b.launch_ptrs([g.data_ptr()], [acc.data_ptr()],
                                             [u.data_ptr()] if u is not None else None,
@@ -184,6 +184,8 @@ def main(argv=None):
     ap.add_argument("--ranks", type=int, default=8)
     ap.add_argument("--ctas", type=int, default=32, help="CTAs per emulated rank")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--in-place", action="store_true",
+                    help="--what single, sparse: the result overwrites the gradient, as in training")
     ap.add_argument("--no-flush", action="store_true",
                     help="--what single: leave L2 (data and code) warm between timed runs")
     a = ap.parse_args(argv)
@@ -194,7 +196,7 @@ def main(argv=None):
         s *= 4
     out = []
     if a.what == "single":
-        run_single(a.alg, a.topo, a.mbytes, a.ctas, a.iters, out, flush_l2=not a.no_flush)
+        run_single(a.alg, a.topo, a.mbytes, a.ctas, a.iters, out, flush_l2=not a.no_flush, in_place=a.in_place)
     if a.what == "generated":
         sweep_generated(a.mbytes, a.iters, out)
     if a.what in ("ops", "all"):

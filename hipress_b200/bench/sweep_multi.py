@@ -142,6 +142,9 @@ def main(argv=None):
                                                "mean_poll_ms": round(p["mean_poll_ms"], 4)}
                                               for p in fused.last_trace_phases()[0]]
                         fused.enable_trace(False)
+                    if a.trace and comp.spec.sparse:
+                        torch.cuda.synchronize()
+                        row["phase_end_ms_rank0"] = [round(x, 4) for x in fused.last_phase_times()]
                     if int(status.abs().sum()) != 0:
                         row["status"] = [w & 0xFFFFFFFF for w in status.tolist()]
                         status.zero_()
