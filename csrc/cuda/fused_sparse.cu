@@ -482,8 +482,6 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
   PUSH(0, ph);
   sp_barrier(cm, cx, sm);
   PUSH(1, ph);
-  // the gradient has been read (it may be the result buffer): clear the result
-  run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
   sp_barrier(cm, cx, sm);
   const bool ovf = any_overflow(cx.ws, units, sm);
   // the candidate list of a unit is short (about as many pairs as are sent): one CTA
@@ -510,6 +508,9 @@ sp_ps_kernel(const SpBucket bk, const HpComm cm, const SpLaunch L) {
     sp_barrier(cm, cx, sm);
     PUSH(7, ph);
   }
+  // The gradient was read two barriers ago (it may be the result buffer): clear the
+  // result here, where the CTAs would otherwise only wait for the peers' pushes.
+  run_units(cx, nseg, sh, [&](int y, uint32_t x, uint32_t nx) { zero_stage(bk, cm, cx, y, x, nx); });
   SRV(0, sh);
   sp_barrier(cm, cx, sm);
   SRV(1, sh);

@@ -31,10 +31,12 @@ from ..parallel.engine import _flat
 from ..parallel.simulate import chunk_range
 
 
-def parameter_checksum(model: torch.nn.Module) -> int:
-    """64-bit wrap-around sum of the raw bits of every parameter and buffer."""
+def parameter_checksum(model: torch.nn.Module, buffers: bool = False) -> int:
+    """64-bit wrap-around sum of the raw bits of every parameter (and, on request,
+    buffer).  Buffers are left out by default: batch-norm running statistics follow each
+    rank's own data and are not synchronised, here as under Horovod."""
     tot = torch.zeros((), dtype=torch.int64, device=next(model.parameters()).device)
-    for t in list(model.parameters()) + list(model.buffers()):
+    for t in list(model.parameters()) + (list(model.buffers()) if buffers else []):
         if t.numel() == 0:
             continue
         flat = t.detach().contiguous().view(-1)
@@ -49,9 +51,9 @@ def parameter_checksum(model: torch.nn.Module) -> int:
     return int(tot.item())
 
 
-def replicas_identical(model: torch.nn.Module) -> bool:
-    """True when every rank's parameters and buffers have the same checksum."""
-    mine = parameter_checksum(model)
+def replicas_identical(model: torch.nn.Module, buffers: bool = False) -> bool:
+    """True when every rank's parameters have the same checksum."""
+    mine = parameter_checksum(model, buffers)
     if comm.size() == 1:
         return True
     every = [None] * comm.size()
