@@ -375,19 +375,6 @@ __device__ __forceinline__ void trace_phase(const HpComm& cm, int E, int ph, Wai
   }
 }
 
-// next tile of this CTA in the encode sequence, walking on across phases; c.phase is
-// the phase of the tile returned
-template <int TOPO>
-__device__ __forceinline__ bool next_encode_item(const BucketDev& bk, int G, int b, int N, int R,
-                                                 Cursor& c, TileRef& out) {
-  bool got = cursor_next(bk, G, b, c, out);
-  while (!got && c.phase + 1 < N) {
-    cursor_begin(bk, G, b, c.phase + 1, phase_spec<TOPO>(c.phase + 1, N, R).chunk, c);
-    got = cursor_next(bk, G, b, c, out);
-  }
-  return got;
-}
-
 template <int ALG, int B, int TOPO>
 __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm& cm,
                                               const FusedParams& fp, FusedSmem& sm, int R, int E,
@@ -402,125 +389,108 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
   bool prod_more = true;
   uint32_t issued = 0, consumed = 0;  // tiles prefetched / used through the bulk pipeline
 
-  // first (non-blocking) loads of the payload a tile merges, one tile ahead: they are
-  // issued before the previous tile is processed, so their L2 round trip is hidden
-  auto issue_in = [&](int ph, const TileRef& t, TileRx<ALG, B>& rx) -> bool {
+  for (int ph = 0; ph < N; ++ph) {
     const PhaseSpec ps = phase_spec<TOPO>(ph, N, R);
-    if (ps.in_slot < 0) return false;
-    const uint8_t* in = my_inbox + (size_t)ps.in_slot * bk.slot_bytes + bk.seg[t.seg].pay_off;
-    if (!dbg_tile_ok<ALG, B>(bk, my_inbox, in, t.t, status, 1u)) {
-      sm.ws.poisoned = 1;
-      return false;
-    }
-    recv_issue<ALG, B>(in, t.t, rx);
-    return true;
-  };
-
-  Cursor cons;
-  cursor_begin(bk, G, b, 0, phase_spec<TOPO>(0, N, R).chunk, cons);
-  TileRef tr, tn;
-  TileRx<ALG, B> rx, rxn;
-  bool have = next_encode_item<TOPO>(bk, G, b, N, R, cons, tr);
-  int ph = cons.phase;
-  bool has_in = have && issue_in(ph, tr, rx);
-  int ps_phase = -1;
-  PhaseSpec ps;
-  uint8_t* dst_base[HP_MAX_RANKS];
-  while (have) {
-    const bool have_n = next_encode_item<TOPO>(bk, G, b, N, R, cons, tn);
-    const int ph_n = cons.phase;
-    const bool has_in_n = have_n && issue_in(ph_n, tn, rxn);
-    if (ph != ps_phase) {
-      ps = phase_spec<TOPO>(ph, N, R);
-      ps_phase = ph;
-#pragma unroll
-      for (int q = 0; q < HP_MAX_RANKS; ++q)
-        dst_base[q] = q < ps.ndst ? reinterpret_cast<uint8_t*>(cm.inbox[(ps.dst0 + q) % N]) +
-                                        (size_t)ps.dst_slot * bk.slot_bytes
-                                  : nullptr;
-    }
-    const SegDev& sg = bk.seg[tr.seg];
-    // top up the prefetch pipeline (stages of finished tiles are free: the
-    // previous tile ended with a CTA barrier)
-    while (prod_more && issued - consumed < kStages) {
-      TileRef pr;
-      if (!next_encode_item<TOPO>(bk, G, b, N, R, prod, pr)) {
-        prod_more = false;
-        break;
-      }
-      const SegDev& psg = bk.seg[pr.seg];
-      const float* pg = psg.g + E * cm.emu_stride_g + pr.off;
-      const float* prr = psg.r ? psg.r + E * cm.emu_stride_r + pr.off : nullptr;
-      if (bulk_ok(pg, prr, pr.m)) {
-        if (threadIdx.x == 0) {
-          const int st = issued % kStages;
-          mbar_expect_tx(&sm.full[st], (prr ? 2u : 1u) * kTile * 4u);
-          bulk_load(sm.g[st], pg, kTile * 4u, &sm.full[st]);
-          if (prr) bulk_load(sm.r[st], prr, kTile * 4u, &sm.full[st]);
-        }
-        ++issued;
-      }
-    }
-    const int m = tr.m;
-    const uint32_t t = tr.t;
-    const float* gp = sg.g + E * cm.emu_stride_g + tr.off;
-    float* rp = sg.r ? sg.r + E * cm.emu_stride_r + tr.off : nullptr;
-    float x[kIter][4];
-    const bool bulk = bulk_ok(gp, rp, m);
-    int st = 0;
-    if (bulk) {
-      st = consumed % kStages;
-      if (!sm.ws.poisoned &&
-          !mbar_wait_bounded(&sm.full[st], (consumed / kStages) & 1, cm.timeout_ns, status,
-                             HP_STATUS_TIMEOUT | (3u << 16) | (b & 255)))
-        sm.ws.poisoned = 1;
-      ++consumed;
-      load_tile_smem(sm.g[st], x);
-    } else {
-      load_tile(gp, m, x);
-    }
-    if (has_in) {
-      float d[kIter][4];
-      recv_finish<ALG, B>(my_inbox + (size_t)ps.in_slot * bk.slot_bytes + sg.pay_off, t, rx, cm, status,
-                          HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
-                          sm.ws, fp.P.tau, d);
-#pragma unroll
-      for (int j = 0; j < kIter; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] + d[j][e];
-    }
-    if (rp) {
-      float rr[kIter][4];
-      if (bulk) load_tile_smem(sm.r[st], rr);
-      else load_tile(rp, m, rr);
-#pragma unroll
-      for (int j = 0; j < kIter; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) x[j][e] = rr[j][e] + x[j][e];
-    }
-    float meta[2];
-    uint32_t frag[kIter];
-    encode_tile<ALG, B>(x, m, fp.P, sg.id, tr.off, fp.P.salt + ps.salt, sm.tile, meta, frag,
-                        rp != nullptr);
-    // after an expired wait the merged input is not a real partial sum: the error
-    // feedback state keeps its last good contents
-    if (rp && !*(volatile int*)&sm.ws.poisoned) store_tile(rp, m, x);
-    uint32_t words[LL<B>::W];
-    pack_words<B>(frag, words);
-    const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
+    Cursor cons;
+    cursor_begin(bk, G, b, ph, ps.chunk, cons);
+    uint8_t* dst_base[HP_MAX_RANKS];
 #pragma unroll
     for (int q = 0; q < HP_MAX_RANKS; ++q)
-      if (q < ps.ndst && dbg_tile_ok<ALG, B>(bk, cm.inbox[(ps.dst0 + q) % N], dst_base[q] + sg.pay_off,
-                                             t, status, 2u))
-        send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
-    __syncthreads();  // the prefetch stage of this tile may be refilled from here on
-    if (!have_n || ph_n != ph)  // this CTA has left phases ph .. ph_n - 1
-      for (int p = ph; p < (have_n ? ph_n : N); ++p) trace_phase(cm, E, p, sm.ws);
-    tr = tn;
-    rx = rxn;
-    ph = ph_n;
-    has_in = has_in_n;
-    have = have_n;
+      dst_base[q] = q < ps.ndst ? reinterpret_cast<uint8_t*>(cm.inbox[(ps.dst0 + q) % N]) +
+                                      (size_t)ps.dst_slot * bk.slot_bytes
+                                : nullptr;
+    const uint8_t* in_base =
+        ps.in_slot >= 0 ? my_inbox + (size_t)ps.in_slot * bk.slot_bytes : nullptr;
+    TileRef tr;
+    while (cursor_next(bk, G, b, cons, tr)) {
+      const SegDev& sg = bk.seg[tr.seg];
+      // top up the prefetch pipeline (stages of finished tiles are free: the
+      // previous tile ended with a CTA barrier)
+      while (prod_more && issued - consumed < kStages) {
+        TileRef pr;
+        bool got = cursor_next(bk, G, b, prod, pr);
+        while (!got && prod.phase + 1 < N) {  // run ahead across phases
+          cursor_begin(bk, G, b, prod.phase + 1, phase_spec<TOPO>(prod.phase + 1, N, R).chunk,
+                       prod);
+          got = cursor_next(bk, G, b, prod, pr);
+        }
+        if (!got) {
+          prod_more = false;
+          break;
+        }
+        const SegDev& psg = bk.seg[pr.seg];
+        const float* pg = psg.g + E * cm.emu_stride_g + pr.off;
+        const float* prr = psg.r ? psg.r + E * cm.emu_stride_r + pr.off : nullptr;
+        if (bulk_ok(pg, prr, pr.m)) {
+          if (threadIdx.x == 0) {
+            const int st = issued % kStages;
+            mbar_expect_tx(&sm.full[st], (prr ? 2u : 1u) * kTile * 4u);
+            bulk_load(sm.g[st], pg, kTile * 4u, &sm.full[st]);
+            if (prr) bulk_load(sm.r[st], prr, kTile * 4u, &sm.full[st]);
+          }
+          ++issued;
+        }
+      }
+      const int m = tr.m;
+      const uint32_t t = tr.t;
+      const float* gp = sg.g + E * cm.emu_stride_g + tr.off;
+      float* rp = sg.r ? sg.r + E * cm.emu_stride_r + tr.off : nullptr;
+      float x[kIter][4];
+      // first loads of the incoming payload go out before anything waits
+      TileRx<ALG, B> rx;
+      const bool has_in = in_base && dbg_tile_ok<ALG, B>(bk, my_inbox, in_base + sg.pay_off, t, status, 1u);
+      if (in_base && !has_in) sm.ws.poisoned = 1;
+      if (has_in) recv_issue<ALG, B>(in_base + sg.pay_off, t, rx);
+      const bool bulk = bulk_ok(gp, rp, m);
+      int st = 0;
+      if (bulk) {
+        st = consumed % kStages;
+        if (!sm.ws.poisoned &&
+            !mbar_wait_bounded(&sm.full[st], (consumed / kStages) & 1, cm.timeout_ns, status,
+                               HP_STATUS_TIMEOUT | (3u << 16) | (b & 255)))
+          sm.ws.poisoned = 1;
+        ++consumed;
+        load_tile_smem(sm.g[st], x);
+      } else {
+        load_tile(gp, m, x);
+      }
+      if (has_in) {
+        float d[kIter][4];
+        recv_finish<ALG, B>(in_base + sg.pay_off, t, rx, cm, status,
+                            HP_STATUS_TIMEOUT | (1u << 16) | ((uint32_t)ps.in_slot << 8) | (b & 255),
+                            sm.ws, fp.P.tau, d);
+#pragma unroll
+        for (int j = 0; j < kIter; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] + d[j][e];
+      }
+      if (rp) {
+        float rr[kIter][4];
+        if (bulk) load_tile_smem(sm.r[st], rr);
+        else load_tile(rp, m, rr);
+#pragma unroll
+        for (int j = 0; j < kIter; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) x[j][e] = rr[j][e] + x[j][e];
+      }
+      float meta[2];
+      uint32_t frag[kIter];
+      encode_tile<ALG, B>(x, m, fp.P, sg.id, tr.off, fp.P.salt + ps.salt, sm.tile, meta, frag,
+                          rp != nullptr);
+      // after an expired wait the merged input is not a real partial sum: the error
+      // feedback state keeps its last good contents
+      if (rp && !*(volatile int*)&sm.ws.poisoned) store_tile(rp, m, x);
+      uint32_t words[LL<B>::W];
+      pack_words<B>(frag, words);
+      const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
+#pragma unroll
+      for (int q = 0; q < HP_MAX_RANKS; ++q)
+        if (q < ps.ndst && dbg_tile_ok<ALG, B>(bk, cm.inbox[(ps.dst0 + q) % N], dst_base[q] + sg.pay_off,
+                                               t, status, 2u))
+          send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
+      __syncthreads();  // the prefetch stage of this tile may be refilled from here on
+    }
+    trace_phase(cm, E, ph, sm.ws);
   }
 }
 
