@@ -145,3 +145,47 @@ def test_new_algorithm_example_trains_on_two_cpu_ranks(tmp_path):
     line = json.loads([row for row in r.stdout.splitlines() if row.startswith("{")][-1])
     assert line["replicas_identical"] and line["backend"] == "host" and line["ranks"] == 2
     assert line["last_loss"] < 0.2 * line["first_loss"] and line["compressed_fraction"] > 0.9
+
+
+# ------------------------------------------------------------ fused target: phase plans
+def _phases(name):
+    from hipress_b200.compll.emit_cuda import generate as gen
+    pse = Path(__file__).resolve().parents[1] / "hipress_b200" / "compll" / "pse"
+    plan = gen((pse / f"{name}.pse").read_text()).fused_plan()
+    if plan is None:
+        return None
+    return [[(it.target if it.kind == "map" else "reduce:" + it.sym.name) for it in ph.items]
+            for ph in plan.phases]
+
+
+def test_fused_plans_of_the_shipped_operators():
+    """One launch per function: maps that only need their own element of what an earlier
+    map wrote share a phase (TBQ: all three), a stage that needs a reduction's result
+    waits behind a barrier (onebit's leftover map, TernGrad's quantising map), and
+    functions with a library-lowered stage keep the staged target."""
+    assert _phases("TbqEncode") == [["residual", "Q", "residual"]]
+    assert _phases("OnebitEncode") == [["residual", "reduce:total", "S"], ["residual"]]
+    assert _phases("TernGradEncode") == [["reduce:hi", "reduce:lo"], ["Q"]]
+    for dec in ("TbqDecode", "OnebitDecode", "TernGradDecode", "TbqDecodeAccumulate"):
+        assert _phases(dec) == [["gradient"]]
+    assert _phases("DgcEncode") is None and _phases("SparseDecodeAccumulate") is None
+
+
+def test_fused_target_starts_a_new_phase_for_reads_at_another_index():
+    from hipress_b200.compll.emit_cuda import generate as gen
+    src = """
+void Shift(float* a, float* b, float* c) {
+    lambda_func first = [&](int i) -> float { return a[i] * 2.0; };
+    b = map(range(a.size), first);
+    lambda_func second = [&](int i) -> float { return b[a.size - 1 - i] + 1.0; };
+    c = map(range(a.size), second);
+}
+"""
+    em = gen(src)
+    plan = em.fused_plan()
+    assert plan is not None and len(plan.phases) == 2      # b is read back to front: barrier
+    body = em.body_source()
+    assert "compll_grid_sync" in body and "Shift_fused_kernel" in body
+    assert "cudaLaunchCooperativeKernel" in em.wrapper_source()
+    staged = gen(src, fuse=False)
+    assert "Shift_map0_kernel" in staged.body_source() and "fused" not in staged.body_source()
