@@ -61,6 +61,17 @@ __device__ __forceinline__ void store_tile(float* __restrict__ p, int m,
   }
 }
 
+// a full tile at a 16-byte aligned address: no per-element checks
+__device__ __forceinline__ void store_tile_full(float* __restrict__ p, const float (&x)[kIter][4]) {
+#pragma unroll
+  for (int j = 0; j < kIter; ++j)
+    reinterpret_cast<float4*>(p)[j * kThreads + (int)threadIdx.x] =
+        make_float4(x[j][0], x[j][1], x[j][2], x[j][3]);
+}
+__device__ __forceinline__ bool tile_is_full_aligned(const float* p, int m) {
+  return m == kTile && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
 // Code fragment = the 4*B bits of the four elements of one float4.
 // Payload bytes that another GPU wrote are read with ld.global.cg (L2 only).
 template <int B>
@@ -222,8 +233,10 @@ __device__ __forceinline__ void encode_tile_impl(float (&x)[kIter][4], int m, co
           c = onebit_code(x[j][e]);
           d = onebit_value(c, meta[0]);
         } else if (ALG == kTbq) {
-          c = tbq_code(x[j][e], P.tau);
-          d = tbq_value(c, P.tau);
+          // tbq_code and tbq_value of it from one pair of compares
+          const bool pos = x[j][e] >= P.tau, neg = x[j][e] <= -P.tau;
+          c = pos ? 3u : (neg ? 2u : 0u);
+          d = pos ? P.tau : (neg ? -P.tau : 0.0f);
         } else {
           c = tern_code(x[j][e], meta[0], scale16, rnd16(rnd.v[e], half), B);
           d = ERR ? tern_value(c, meta[0], gap) : 0.0f;

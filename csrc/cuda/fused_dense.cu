@@ -213,12 +213,14 @@ __device__ __forceinline__ void recv_issue(const uint8_t* base, uint32_t t, Tile
 template <int ALG, int B>
 __device__ __forceinline__ void recv_finish(const uint8_t* base, uint32_t t, TileRx<ALG, B>& rx,
                                             const HpComm& cm, uint32_t* status, uint32_t code,
-                                            WaitState& ws, float tau, float (&d)[kIter][4]) {
+                                            WaitState& ws, float tau, float (&d)[kIter][4],
+                                            float meta_scale = 1.0f) {
   const uint2* tb = tile_base<ALG, B>(const_cast<uint8_t*>(base), t);
   float meta[2] = {0.0f, 0.0f};
 #pragma unroll
   for (int k = 0; k < MetaOf<ALG>::N; ++k)
     meta[k] = __uint_as_float(ll_finish(tb + k, rx.m[k], cm, status, code, ws));
+  if (ALG == kOnebit) meta[0] = meta[0] * meta_scale;  // see decode_phase
   uint32_t w[LL<B>::W], f[kIter];
 #pragma unroll
   for (int k = 0; k < LL<B>::W; ++k)
@@ -393,12 +395,7 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
     const PhaseSpec ps = phase_spec<TOPO>(ph, N, R);
     Cursor cons;
     cursor_begin(bk, G, b, ph, ps.chunk, cons);
-    uint8_t* dst_base[HP_MAX_RANKS];
-#pragma unroll
-    for (int q = 0; q < HP_MAX_RANKS; ++q)
-      dst_base[q] = q < ps.ndst ? reinterpret_cast<uint8_t*>(cm.inbox[(ps.dst0 + q) % N]) +
-                                      (size_t)ps.dst_slot * bk.slot_bytes
-                                : nullptr;
+    const size_t dst_off = (size_t)ps.dst_slot * bk.slot_bytes;
     const uint8_t* in_base =
         ps.in_slot >= 0 ? my_inbox + (size_t)ps.in_slot * bk.slot_bytes : nullptr;
     TileRef tr;
@@ -479,15 +476,24 @@ __device__ __forceinline__ void encode_phases(const BucketDev& bk, const HpComm&
                           rp != nullptr);
       // after an expired wait the merged input is not a real partial sum: the error
       // feedback state keeps its last good contents
-      if (rp && !*(volatile int*)&sm.ws.poisoned) store_tile(rp, m, x);
+      const bool bad = *(volatile int*)&sm.ws.poisoned != 0;
+      if (rp && !bad) {
+        if (bulk) store_tile_full(rp, x);
+        else store_tile(rp, m, x);
+      }
       uint32_t words[LL<B>::W];
       pack_words<B>(frag, words);
-      const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
-#pragma unroll
-      for (int q = 0; q < HP_MAX_RANKS; ++q)
-        if (q < ps.ndst && dbg_tile_ok<ALG, B>(bk, cm.inbox[(ps.dst0 + q) % N], dst_base[q] + sg.pay_off,
-                                               t, status, 2u))
-          send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
+      const uint32_t ep = cm.epoch | (bad ? kGaveUp : 0u);
+      // one destination on a hop, every rank on the last one (a rolled loop: the
+      // broadcast is one phase in N)
+#pragma unroll 1
+      for (int q = 0; q < ps.ndst; ++q) {
+        int d = ps.dst0 + q;
+        if (d >= N) d -= N;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[d]) + dst_off + sg.pay_off;
+        if (dbg_tile_ok<ALG, B>(bk, cm.inbox[d], dst, t, status, 2u))
+          send_tile<ALG, B>(dst, t, words, meta, ep);
+      }
       __syncthreads();  // the prefetch stage of this tile may be refilled from here on
     }
     trace_phase(cm, E, ph, sm.ws);
@@ -532,14 +538,23 @@ __device__ __forceinline__ void decode_phase(const BucketDev& bk, const HpComm& 
       if (u < cnt) {
         const SegDev& sg = bk.seg[tr[u].seg];
         float x[kIter][4];
-        recv_finish<ALG, B>(sp + sg.pay_off, tr[u].t, rx[u], cm, status, code, sm.ws, fp.P.tau, x);
+        // onebit and TBQ decode to +-level or 0, so level * (1/N) is the same float
+        // whether the level or the element is scaled; TernGrad's min + q * gap is not
+        constexpr bool kFold = ALG != kTernGrad;
+        recv_finish<ALG, B>(sp + sg.pay_off, tr[u].t, rx[u], cm, status, code, sm.ws,
+                            kFold ? fp.P.tau * fp.inv_n : fp.P.tau, x, kFold ? fp.inv_n : 1.0f);
+        if (!kFold) {
 #pragma unroll
-        for (int j = 0; j < kIter; ++j)
+          for (int j = 0; j < kIter; ++j)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] * fp.inv_n;
+            for (int e = 0; e < 4; ++e) x[j][e] = x[j][e] * fp.inv_n;
+        }
         // a tile whose payload never arrived is left as it was (the local gradient)
-        if (!*(volatile int*)&sm.ws.poisoned)
-          store_tile(sg.out + E * cm.emu_stride_out + tr[u].off, tr[u].m, x);
+        if (!*(volatile int*)&sm.ws.poisoned) {
+          float* op = sg.out + E * cm.emu_stride_out + tr[u].off;
+          if (tile_is_full_aligned(op, tr[u].m)) store_tile_full(op, x);
+          else store_tile(op, tr[u].m, x);
+        }
       }
     }
   }
@@ -604,12 +619,7 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
     Cursor cur;
     cursor_begin(bk, G, b, N, R, cur);
     TileRef tr;
-    uint8_t* dst_base[HP_MAX_RANKS];
-#pragma unroll
-    for (int q = 0; q < HP_MAX_RANKS; ++q)
-      dst_base[q] = q < N ? reinterpret_cast<uint8_t*>(cm.inbox[(R + q) % N]) +
-                                (size_t)(N + R) * bk.slot_bytes
-                          : nullptr;
+    const size_t dst_off = (size_t)(N + R) * bk.slot_bytes;
     while (cursor_next(bk, G, b, cur, tr)) {
       const SegDev& sg = bk.seg[tr.seg];
       const int m = tr.m;
@@ -651,14 +661,22 @@ ps_dense_kernel(const BucketDev bk, const HpComm cm, const FusedParams fp) {
       uint32_t frag[kIter];
       encode_tile<ALG, B>(x, m, fp.P, sg.id, (size_t)R * sg.chunk + coff,
                           fp.P.salt + (uint32_t)(R * 256 + 1), s, meta, frag, rp != nullptr);
-      if (rp && !*(volatile int*)&sm.ws.poisoned) store_tile(rp, m, x);
+      const bool bad = *(volatile int*)&sm.ws.poisoned != 0;
+      if (rp && !bad) {
+        if (tile_is_full_aligned(rp, m)) store_tile_full(rp, x);
+        else store_tile(rp, m, x);
+      }
       uint32_t words[LL<B>::W];
       pack_words<B>(frag, words);
-      const uint32_t ep = cm.epoch | (*(volatile int*)&sm.ws.poisoned ? kGaveUp : 0u);
-#pragma unroll
-      for (int q = 0; q < HP_MAX_RANKS; ++q)
-        if (q < N && dbg_tile_ok<ALG, B>(bk, cm.inbox[(R + q) % N], dst_base[q] + sg.pay_off, t, status, 5u))
-          send_tile<ALG, B>(dst_base[q] + sg.pay_off, t, words, meta, ep);
+      const uint32_t ep = cm.epoch | (bad ? kGaveUp : 0u);
+#pragma unroll 1
+      for (int q = 0; q < N; ++q) {
+        int d = R + q;
+        if (d >= N) d -= N;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(cm.inbox[d]) + dst_off + sg.pay_off;
+        if (dbg_tile_ok<ALG, B>(bk, cm.inbox[d], dst, t, status, 5u))
+          send_tile<ALG, B>(dst, t, words, meta, ep);
+      }
     }
     trace_phase(cm, E, N, sm.ws);
   }
