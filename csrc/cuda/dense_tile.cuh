@@ -163,10 +163,16 @@ __device__ __forceinline__ void decode_frag(uint32_t frag, const float (&meta)[2
   if (ALG == kTernGrad) gap = tern_gap(meta[0], meta[1], B);
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
-    const uint32_t c = (frag >> (e * B)) & mask;
-    if (ALG == kOnebit) d[e] = onebit_value(c, meta[0]);
-    else if (ALG == kTbq) d[e] = tbq_value(c, tau);
-    else d[e] = tern_value(c, meta[0], gap);
+    if (ALG == kTbq) {
+      // tbq_value of the 2-bit code at bits 2e, 2e+1 by testing the bits in place
+      // (bit 1: non-zero level, bit 0: positive)
+      const bool nz = (frag & (2u << (e * B))) != 0u, pos = (frag & (1u << (e * B))) != 0u;
+      d[e] = nz ? (pos ? tau : -tau) : 0.0f;
+    } else {
+      const uint32_t c = (frag >> (e * B)) & mask;
+      if (ALG == kOnebit) d[e] = onebit_value(c, meta[0]);
+      else d[e] = tern_value(c, meta[0], gap);
+    }
   }
 }
 

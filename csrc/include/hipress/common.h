@@ -183,7 +183,8 @@ HP_HD int32_t f2i_floor_sat(float t) {
 #endif
 }
 HP_HD uint32_t tern_code(float x, float mn, float scale16, uint32_t u16, int bits) {
-  if (!(scale16 > 0.0f)) return 0u;
+  // scale16 == 0 (a constant tile) needs no test of its own: the product is 0 or NaN,
+  // both convert to 0, and (0 + u16) >> 16 == 0
   const uint32_t t = (uint32_t)f2i_floor_sat((x - mn) * scale16);
   const uint32_t q = (t + u16) >> 16;
   const uint32_t qmax = (1u << bits) - 1u;
