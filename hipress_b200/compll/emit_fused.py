@@ -232,14 +232,14 @@ class FusedGen:
                 return fwd[sym.name]
             if sym.bits is None:
                 need_in[sym.name] = None
-                return f"in_{sym.name}[e]"
+                return f"in_{sym.name}[u][e]"
             return frag_value(sym)
 
         def frag_value(sym):
             # a packed input read at the own index: the group's fragment is loaded once
             need_frag[sym.name] = None
             b = f"(uint32_t)({em.expr(sym.bits, set())})"
-            return f"((fr_{sym.name} >> (e * {b})) & ((1u << {b}) - 1u))"
+            return f"((fr_{sym.name}[u] >> (e * {b})) & ((1u << {b}) - 1u))"
 
         def random_hook(site):
             sites.append(site)
@@ -251,7 +251,7 @@ class FusedGen:
             s = em.syms[vec]
             if s.bits is None:
                 need_in[vec] = None
-                return f"in_{vec}[e]"
+                return f"in_{vec}[u][e]"
             return frag_value(s)
 
         em._index_hook, em._random_hook = index_hook, random_hook
@@ -310,11 +310,16 @@ class FusedGen:
             em._index_hook = em._random_hook = None
             em._own = None
             em._return_to = None
-        loads = [f"      {C_TYPES[em.syms[v].type.name]} in_{v}[4];\n"
-                 f"      compll_load4(c.v_{v}, i0, count, in_{v});" for v in need_in]
+        # U groups of four elements per thread and trip: every load of a trip is issued
+        # before the first result is computed (a map only reads its own elements of the
+        # vectors it also writes, so hoisting the loads over the stores is safe)
+        U = 4 if len(need_in) <= 2 else 2
+        larr = [f"      {C_TYPES[em.syms[v].type.name]} in_{v}[{U}][4];" for v in need_in] + \
+               [f"      uint32_t fr_{v}[{U}];" for v in need_frag]
+        loads = [f"        compll_load4(c.v_{v}, i0, count, in_{v}[u]);" for v in need_in]
         for v in need_frag:
             b = f"(uint32_t)({em.expr(em.syms[v].bits, set())})"
-            loads.append(f"      const uint32_t fr_{v} = compll_load_frag(c.v_{v}, (c.n_{v} * {b} + 7) / 8, q, {b});")
+            loads.append(f"        fr_{v}[u] = compll_load_frag(c.v_{v}, (c.n_{v} * {b} + 7) / 8, q, {b});")
         rngs = [f"      const hipress::Philox4 rg{s} = compll_rand4(c.seed, q, {s}u);" for s in sorted(set(sites))]
         reds = [it.sym for it in ph.items if it.kind == "reduce"]
         acc_init = [f"    {C_TYPES[s.type.name]} acc_{s.name} = ({C_TYPES[s.type.name]})"
@@ -334,10 +339,22 @@ class FusedGen:
 {header}    const uint64_t count = {ph.count};
     const uint64_t groups = (count + 3) / 4;
 {nl.join(acc_init)}
-    for (uint64_t qb = (uint64_t)blockIdx.x * blockDim.x; qb < groups; qb += (uint64_t)gridDim.x * blockDim.x) {{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t qb0 = (uint64_t)blockIdx.x * blockDim.x; qb0 < groups; qb0 += stride * {U}) {{
+{nl.join(larr)}
+#pragma unroll
+      for (int u = 0; u < {U}; ++u) {{   // past the end the loads return zeros and touch nothing
+        const uint64_t q = qb0 + u * stride + threadIdx.x;
+        const uint64_t i0 = q * 4;
+        (void)q; (void)i0;
+{nl.join(loads)}
+      }}
+#pragma unroll
+      for (int u = 0; u < {U}; ++u) {{
+      const uint64_t qb = qb0 + u * stride;   // the same for the whole block
+      if (qb >= groups) break;
       const uint64_t q = qb + threadIdx.x;
       const uint64_t i0 = q * 4;
-{nl.join(loads)}
 {nl.join(rngs)}
 {nl.join(decls)}
 #pragma unroll
@@ -347,6 +364,7 @@ class FusedGen:
 {nl.join(body)}
       }}
 {nl.join(stores)}
+      }}
     }}
 {self._block_reduce(reds)}  }}
 """
