@@ -310,10 +310,14 @@ class FusedGen:
             em._index_hook = em._random_hook = None
             em._own = None
             em._return_to = None
-        # U groups of four elements per thread and trip: every load of a trip is issued
-        # before the first result is computed (a map only reads its own elements of the
-        # vectors it also writes, so hoisting the loads over the stores is safe)
-        U = 4 if len(need_in) <= 2 else 2
+        # U groups of four elements per thread and trip, every load of a trip issued before
+        # the first result is computed (a map only reads its own elements of the vectors
+        # it also writes, so hoisting the loads over the stores is safe).  Measured at
+        # 256 MB: a phase whose only inputs are packed fragments (the decodes, bound by
+        # their stores) gains from four groups in flight (TbqDecode 0.075 -> 0.061 ms,
+        # OnebitDecode 0.069 -> 0.057 ms); a phase that also streams a float vector in
+        # (decode-accumulate, the encoders) lost up to 25 % and keeps one.
+        U = 4 if not need_in else 1
         larr = [f"      {C_TYPES[em.syms[v].type.name]} in_{v}[{U}][4];" for v in need_in] + \
                [f"      uint32_t fr_{v}[{U}];" for v in need_frag]
         loads = [f"        compll_load4(c.v_{v}, i0, count, in_{v}[u]);" for v in need_in]
