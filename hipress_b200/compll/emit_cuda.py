@@ -536,8 +536,17 @@ __global__ void __launch_bounds__(256) {name}_map{idx}_kernel({self.kernel_param
             self.rand_sites = 0
             maps, reduces = FusedGen(fused).kernel_source(), ""
         else:
-            maps = "\n".join(self.map_kernel(i, t, m, i == len(self.maps) - 1)
-                             for i, (t, m) in enumerate(self.maps))
+            # staged target; runs of maps between library calls may still share a kernel
+            segs = self.segments()
+            in_seg = {self.stages[k][1] for i0, cnt, _ in segs for k in range(i0, i0 + cnt)}
+            last_map = len(self.maps) - 1
+            maps = "\n".join(self.map_kernel(i, t, m, i == last_map)
+                             for i, (t, m) in enumerate(self.maps) if i not in in_seg)
+            if segs:
+                from .emit_fused import FusedGen
+                for si, (i0, cnt, plan) in enumerate(segs):
+                    has_last = any(self.stages[k][1] == last_map for k in range(i0, i0 + cnt))
+                    maps += FusedGen(plan, tag=f"seg{si}", write_header=has_last).kernel_source()
             reduces = "\n".join(self.reduce_kernel(gi, st[1]) for gi, st in enumerate(self.stages)
                                 if st[0] == "reduce")
         src_comment = "\n".join("//   " + l for l in self.fn.source.strip().splitlines())
@@ -572,6 +581,16 @@ namespace compll_gen_{name} {{
             self._fused_plan = plan if plan.ok else None
         return self._fused_plan
 
+    def segments(self):
+        """Fusable runs of maps of a function that keeps the staged target (see
+        emit_fused.fused_segments); empty when the whole function is one launch."""
+        if not getattr(self, "fuse", True) or self.fused_plan() is not None:
+            return []
+        if not hasattr(self, "_segments"):
+            from .emit_fused import fused_segments
+            self._segments = fused_segments(self)
+        return self._segments
+
     def wrapper_source(self) -> str:
         """``extern "C"`` launcher (``-w``): stream-ordered, no host synchronisation."""
         name = self.fn.name
@@ -600,7 +619,18 @@ namespace compll_gen_{name} {{
                 if sy.kind == "derived" and not self._depends_on_reduced(sy.expr) and \
                         not self._depends_on_extracted(sy.expr):
                     rows.append(f"  h.v_{sname} = ({C_TYPES[sy.type.name]})({self.expr(sy.expr, set(), 'h.')});")
+        seg_at = {i0: (si, cnt, plan) for si, (i0, cnt, plan) in enumerate(self.segments())}
+        skip = 0
         for gi, st in enumerate(self.stages):
+            if skip:
+                skip -= 1
+                continue
+            if gi in seg_at:
+                from .emit_fused import FusedGen
+                si, cnt, plan = seg_at[gi]
+                rows.append(FusedGen(plan, tag=f"seg{si}").launch_rows())
+                skip = cnt - 1
+                continue
             if st[0] == "topk":
                 _, target, call = st
                 vec = call.args[0].id

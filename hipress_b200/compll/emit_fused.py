@@ -22,7 +22,8 @@ one persistent kernel that runs them back to back:
 * ``random<float>`` costs one Philox call per four elements.
 
 Functions with library-lowered stages (``topk``, ``scatter``) keep the staged
-target.  The rules this replaces: one ``thrust::transform`` per map with one
+target for those stages; a run of maps between them still becomes one kernel
+(``fused_segments``: DgcEncode's two state updates are one pass).  The rules this replaces: one ``thrust::transform`` per map with one
 thread per output byte and a serial pack loop (src/CompLL/GCGen/tree.py:197-244,
 unit.py:469-482 of mark14wu/hipress).
 """
@@ -70,8 +71,9 @@ class Phase:
 class FusedPlan:
     """Phase plan of one function; ``ok`` is False when the staged target must be used."""
 
-    def __init__(self, em: Emitter):
+    def __init__(self, em: Emitter, stages: list | None = None):
         self.em = em
+        self.stages = list(em.stages if stages is None else stages)
         self.phases: list[Phase] = []
         self.ok = True
         self.why = ""
@@ -140,7 +142,7 @@ class FusedPlan:
                 self.phases.append(cur)
             cur = None
 
-        for st in em.stages:
+        for st in self.stages:
             if st[0] in ("topk", "scatter"):
                 raise _NoFusion("library-lowered stage")
             if st[0] == "reduce":
@@ -195,12 +197,42 @@ class _NoFusion(Exception):
     pass
 
 
+def fused_segments(em: Emitter) -> list:
+    """For a function that keeps the staged target because of a library-lowered stage:
+    the runs of consecutive ``map`` stages between the library calls that can still be
+    one kernel.  Returns [(index of the run's first stage, number of stages, FusedPlan)].
+    Kept simple on purpose: the function has no reduction, the run has at least two
+    maps, none of them draws random numbers (the call sites are numbered per target)
+    and the run plans as a single phase, so the kernel needs no grid barrier."""
+    if em.reduces:
+        return []
+    out, i, n = [], 0, len(em.stages)
+    while i < n:
+        j = i
+        while j < n and em.stages[j][0] == "map":
+            j += 1
+        run = em.stages[i:j]
+        if len(run) >= 2:
+            rnd = False
+            for st in run:
+                lam = em.syms.get(getattr(em.maps[st[1]][1].fn, "id", ""), None)
+                if lam is None or any(isinstance(x, F.Random) for x in _walk(lam.expr.body)):
+                    rnd = True
+            plan = None if rnd else FusedPlan(em, run)
+            if plan is not None and plan.ok and len(plan.phases) == 1:
+                out.append((i, len(run), plan))
+        i = max(j, i + 1)
+    return out
+
+
 class FusedGen:
     """Emits the fused kernel and its launch for a plan that is ``ok``."""
 
-    def __init__(self, plan: FusedPlan):
+    def __init__(self, plan: FusedPlan, tag: str = "fused", write_header: bool = True):
         self.plan, self.em = plan, plan.em
         self.name = self.em.fn.name
+        self.tag = tag                    # kernel name: <function>_<tag>_kernel
+        self.write_header = write_header  # the launch that runs last writes the concat headers
 
     # ------------------------------------------------------------ helpers
     def _apply(self, r: F.Reduce, a: str, b: str) -> str:
@@ -330,7 +362,7 @@ class FusedGen:
                     f"({em.expr(s.expr.init, set())});" for s in reds]
         nl = "\n"
         header = ""
-        if last:
+        if last and self.write_header:
             rows = []
             for tname, fields, _ in em.concats:
                 for fname, off in fields:
@@ -443,7 +475,7 @@ class FusedGen:
 """
         return f"""
 // One launch for the whole function: {len(phases)} phase(s){', grid barriers in between' if len(phases) > 1 else ''}.
-__global__ void __launch_bounds__(256) {name}_fused_kernel({em.kernel_params()}, float* partials,
+__global__ void __launch_bounds__(256) {name}_{self.tag}_kernel({em.kernel_params()}, float* partials,
                                                        unsigned int* sync) {{
   __shared__ float sh[{nred}][8];
   float red[{nred}];
@@ -470,7 +502,7 @@ __global__ void __launch_bounds__(256) {name}_fused_kernel({em.kernel_params()},
     if (cap[dev] == 0) {{
       int sms = 0, per = 0;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, compll_gen_{name}::{name}_fused_kernel, 256, 0);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, compll_gen_{name}::{name}_{self.tag}_kernel, 256, 0);
       cap[dev] = per * sms > 0 ? per * sms : 1;
     }}
     uint64_t most = work;
@@ -482,7 +514,7 @@ __global__ void __launch_bounds__(256) {name}_fused_kernel({em.kernel_params()},
     unsigned int* sync = ticket;
     void* args[] = {{{', '.join('(void*)&' + a for a in self._arg_names())}, (void*)&partials, (void*)&sync}};
     cudaError_t e = {'cudaLaunchCooperativeKernel' if coop else 'cudaLaunchKernel'}(
-        (const void*)compll_gen_{name}::{name}_fused_kernel, dim3(fgrid), dim3(256), args, 0, st);
+        (const void*)compll_gen_{name}::{name}_{self.tag}_kernel, dim3(fgrid), dim3(256), args, 0, st);
     if (e != cudaSuccess) return (int)e;
   }}"""
 

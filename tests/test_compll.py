@@ -171,6 +171,27 @@ def test_fused_plans_of_the_shipped_operators():
     assert _phases("DgcEncode") is None and _phases("SparseDecodeAccumulate") is None
 
 
+def test_maps_around_a_library_stage_still_share_a_kernel():
+    """DgcEncode = two state-update maps + the library's exact top-k: the maps are one
+    kernel (one pass over u, v and g), launched right before the library call."""
+    from hipress_b200.compll.emit_cuda import generate as gen
+    pse = Path(__file__).resolve().parents[1] / "hipress_b200" / "compll" / "pse"
+    em = gen((pse / "DgcEncode.pse").read_text())
+    segs = em.segments()
+    assert [(i0, cnt) for i0, cnt, _ in segs] == [(0, 2)]
+    assert [[it.target for it in ph.items] for ph in segs[0][2].phases] == [["momentum_u", "accum_v"]]
+    body, wrap = em.body_source(), em.wrapper_source()
+    assert "DgcEncode_seg0_kernel" in body and "_map0_kernel" not in body and "_map1_kernel" not in body
+    assert wrap.index("DgcEncode_seg0_kernel") < wrap.index("hp_cuda_sparse_encode(4")
+    assert "cudaLaunchCooperativeKernel" not in wrap        # one phase: no grid barrier
+    # a single map next to the library call stays as it was
+    one = gen((pse / "GradDropEncode.pse").read_text())
+    assert one.segments() == [] and "_map0_kernel" in one.body_source()
+    # and the staged target is still available
+    staged = gen((pse / "DgcEncode.pse").read_text(), fuse=False)
+    assert staged.segments() == [] and "_map1_kernel" in staged.body_source()
+
+
 def test_fused_target_starts_a_new_phase_for_reads_at_another_index():
     from hipress_b200.compll.emit_cuda import generate as gen
     src = """
