@@ -179,7 +179,8 @@ def timed_e2e(job, hosts, steps, sync_all, N, dev):
 def main():
     a = parse()
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:     # one line per job, also under torchrun
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}), flush=True)
         return 0
     import torch
     import torch.distributed as dist
