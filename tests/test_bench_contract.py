@@ -19,6 +19,18 @@ def test_reference_arm_reports_unavailable():
     assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
 
 
+def test_reference_arm_prints_one_line_per_job_under_torchrun():
+    """For N > 1 the arm is launched like the product arm, one process per GPU: only
+    rank 0 answers."""
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29587", str(ROOT / "bench.py"),
+                          "--impl", "reference", "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1 and json.loads(lines[0])["impl"] == "reference"
+
+
 def test_graft_entry_has_build_and_smoke():
     sys.path.insert(0, str(ROOT))
     import __graft_entry__ as g
