@@ -83,7 +83,7 @@ def test_fit_helpers():
 
 
 @pytest.mark.parametrize("alg", ["onebit", "tbq", "terngrad", "dgc", "graddrop"])
-@pytest.mark.parametrize("n", [2, 8])
+@pytest.mark.parametrize("n", [2, 4, 8])
 def test_shipped_profiles_give_sane_vgg19_plans(alg, n, vgg19_gradient_list):
     from hipress_b200.secopa import read_gradient_list
     prof = CostProfile.from_json((PROFILES / f"b200_{alg}_n{n}.json").read_text())
