@@ -170,6 +170,25 @@ def sweep_generated(mbytes, iters, out):
                    "peak_source": peaks["source"]}
             out.append(row)
             print(json.dumps(row), flush=True)
+    # DGC encode: the generated function is one kernel for both state updates plus the
+    # run-time library's exact top-k; the hand-written path folds the updates into the
+    # selection's histogram pass
+    ratio, m = 0.001, 0.9
+    k = int(n * ratio) + 16      # the function rounds ratio * n up in fp32; the buffer may be larger
+    hand = Compressor("dgc", ratio=ratio)
+    st = hand.new_state(n, "cuda")
+    pay = torch.empty(hand.payload_bytes(n), dtype=torch.uint8, device="cuda")
+    comp = torch.zeros(16 + 2 * ((4 * k + 15) // 16 * 16), dtype=torch.uint8, device="cuda")
+    u, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    enc = load_op("DgcEncode")
+    tg = time_cuda(lambda: enc(g, u, v, comp, ratio, m), iters=iters, flush=flush)
+    ws = hand.new_workspace("cuda", n)
+    th = time_cuda(lambda: hand.encode(g, st, out=pay, workspace=ws), iters=iters, flush=flush)
+    row = {"operator": "DgcEncode", "mbytes": mbytes, "generated_ms": round(tg["median_ms"], 5),
+           "hand_ms": round(th["median_ms"], 5),
+           "generated_over_hand": round(tg["median_ms"] / th["median_ms"], 3), "peak_source": peaks["source"]}
+    out.append(row)
+    print(json.dumps(row), flush=True)
 
 
 def main(argv=None):
